@@ -1,0 +1,85 @@
+/*
+ * C ABI of librocm_dev_b200.so - B200 (sm_100a) FP8 GEMM family, sum-reduce,
+ * grid barrier and FP8-encoded allreduce.
+ *
+ * Conventions shared by every entry point:
+ *   - all data pointers are DEVICE pointers owned by the caller; nothing is
+ *     allocated per call and nothing is freed;
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default
+ *     stream, which is what the reference launchers use); calls are
+ *     asynchronous and return after the launch;
+ *   - the return value is an rdb_status.  Codes 0..6 keep the meaning of the
+ *     reference's SkinnyGemmReturnCode (projects/skinny_gemm/
+ *     skinny_gemm_caller.cu:9-17); larger codes are new.  No entry point calls
+ *     exit();
+ *   - fp8 means OCP e4m3fn bytes (bias 7, max 448); bf16 results are written
+ *     as raw 16-bit patterns;
+ *   - a device-side wait that runs out of its time budget stores
+ *     RDB_DEVICE_TIMEOUT in a per-device status word read (and cleared) by
+ *     rdb_device_status().
+ *
+ * Paths are given relative to the reference project root.
+ */
+#ifndef ROCM_DEV_B200_H
+#define ROCM_DEV_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum rdb_status {
+    RDB_SUCCESS = 0,
+    RDB_M_ABOVE_WARPTILE_M = 1,            /* M larger than the kernel family supports */
+    RDB_N_NOT_EVEN = 2,
+    RDB_K_NOT_DIVISIBLE_BY_WARPTILE_K = 3, /* K (or a row pitch) breaks the 16-byte TMA rule */
+    RDB_TOO_MANY_WARPS = 4,
+    RDB_QSIZE_TOO_SMALL = 5,
+    RDB_INVALID_CONFIG = 6,
+    RDB_BAD_ALIGNMENT = 7,                 /* a base pointer is not 16-byte aligned */
+    RDB_BAD_SHAPE = 8,                     /* non-positive or unsupported extent */
+    RDB_CUDA_ERROR = 9,                    /* a CUDA runtime / driver call failed */
+    RDB_DEVICE_TIMEOUT = 10,               /* a bounded device-side wait ran out */
+    RDB_SIZE_ABOVE_LIMIT = 11
+} rdb_status;
+
+/* Human-readable name of a status code (static storage). */
+const char *rdb_status_string(int status);
+
+/* Synchronises the current device, returns the status word device code wrote
+ * since the last call (RDB_SUCCESS if none) and clears it. */
+int rdb_device_status(void);
+
+/* Library version string and the SM architecture the kernels were built for. */
+const char *rdb_version(void);
+
+/* ------------------------------------------------------------ skinny GEMM
+ * D[M,N] = bf16( (A . B^T) * scale_a[0] * scale_b[0] ),  M <= 32.
+ *   A [M,K] row-major fp8; B [N,K] fp8, K-contiguous with row pitch ldb bytes;
+ *   scale_a / scale_b: device pointers to one fp32 each; D [M,N] row-major
+ *   bf16, OVERWRITTEN (equals the reference result under its zeroed-D
+ *   precondition).
+ * Replaces skinny_gemm_fastpath (projects/skinny_gemm/skinny_gemm_caller.cu:
+ * 343-405) and skinny_gemm (same file :20-340), whose output type was fp16 and
+ * which took a single scale; the hint arguments of the latter are accepted by
+ * rdb_skinny_gemm_fp8_hinted below. */
+int rdb_skinny_gemm_fp8(const uint8_t *A, const uint8_t *B, const float *scale_a, const float *scale_b,
+                        uint16_t *D, int M, int N, int K, int ldb, void *stream);
+
+/* Same contraction with the reference's tuning arguments
+ * (projects/skinny_gemm/skinny_gemm_caller.cu:20-43).  split_k (1..8, 0 =
+ * automatic) and qsize (pipeline stages, 0 = automatic) steer the kernel; the
+ * producer / consumer wave counts, b_lanes, op_m and ops are validated with
+ * the reference's rules (same return codes) and otherwise ignored. */
+int rdb_skinny_gemm_fp8_hinted(const uint8_t *A, const uint8_t *B, const float *scale_a, const float *scale_b,
+                               uint16_t *D, int M, int N, int K, int ldb, int split_k, int A_producers,
+                               int B_producers, int consumers, int b_lanes, int qsize, int op_m, int ops,
+                               void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* ROCM_DEV_B200_H */

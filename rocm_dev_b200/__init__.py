@@ -1,0 +1,14 @@
+"""B200-native (sm_100a) FP8 GEMM family, sum-reduce and FP8-encoded allreduce.
+
+Host-side mirror of the reference project's launcher interface over a C ABI
+(include/rocm_dev_b200.h).  PyTorch is used for device memory and streams only.
+"""
+from ._lib import LibraryMissing, RdbError, lib, status_string  # noqa: F401
+from .skinny_gemm import (  # noqa: F401
+    HFRK_skinny_gemm,
+    SkinnyGemmReturnCode,
+    skinny_gemm,
+    skinny_gemm_fastpath,
+    skinny_gemm_fp8,
+    skinny_gemm_fp8_host,
+)

@@ -1,0 +1,65 @@
+"""ctypes binding of the C ABI declared in include/rocm_dev_b200.h.
+
+There is no fallback: if the shared library is missing the import of any
+operator fails with an error that says how to build it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+from .build import LIB_PATH
+
+_lib = None
+
+u8p = C.c_void_p
+f32p = C.c_void_p
+vp = C.c_void_p
+i = C.c_int
+
+_SIGNATURES = {
+    "rdb_status_string": (C.c_char_p, [i]),
+    "rdb_device_status": (i, []),
+    "rdb_version": (C.c_char_p, []),
+    "rdb_skinny_gemm_fp8": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, vp]),
+    "rdb_skinny_gemm_fp8_hinted": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, i, i, i, i, i, i, i, i, vp]),
+}
+
+
+class LibraryMissing(RuntimeError):
+    pass
+
+
+def lib() -> C.CDLL:
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise LibraryMissing(
+                f"{LIB_PATH} not found: build it with `python -m rocm_dev_b200.build` "
+                "(there is no CPU or PyTorch fallback)")
+        handle = C.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)
+            fn.restype = res
+            fn.argtypes = args
+        _lib = handle
+    return _lib
+
+
+def exported_symbols() -> list[str]:
+    return list(_SIGNATURES)
+
+
+def status_string(code: int) -> str:
+    return lib().rdb_status_string(int(code)).decode()
+
+
+class RdbError(RuntimeError):
+    def __init__(self, code: int, where: str):
+        self.code = int(code)
+        super().__init__(f"{where}: status {code} ({status_string(code)})")
+
+
+def check(code: int, where: str) -> None:
+    if code != 0:
+        raise RdbError(code, where)

@@ -1,0 +1,37 @@
+// Host-side helpers shared by the launchers: status codes, the per-device
+// status word device code reports into, and TMA tensor-map construction
+// through the driver entry point (no link-time dependency on libcuda, so the
+// library also loads on a machine without a GPU driver).
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/rocm_dev_b200.h"
+
+namespace rdb {
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceInfo {
+    bool ready = false;
+    int sm_count = 0;
+    int* status_host = nullptr;  // pinned, mapped host word
+    int* status_dev = nullptr;   // device alias of the same word
+};
+
+// Per-device facts and the status word; created on first use with that device
+// current.  Returns nullptr (and sets *err) when a CUDA call fails.
+DeviceInfo* device_info(int* err);
+
+// Encodes a 2-D tiled tensor map over a row-major [rows, cols] array of
+// `elem_bytes`-sized elements with row pitch `pitch_bytes`.  box = {box_cols,
+// box_rows}.  swizzle is a CUtensorMapSwizzle value.
+int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes, uint64_t rows,
+                 uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swizzle,
+                 CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace rdb

@@ -1,0 +1,160 @@
+"""Host side of the skinny FP8 GEMM, mirroring the reference launchers.
+
+Reference interface (paths within the reference project):
+  - ``skinny_gemm_fastpath(A, B, D, scale_tensor, m, n, k)`` -
+    projects/skinny_gemm/skinny_gemm_caller.cu:343-405
+  - ``skinny_gemm(A, B, D, scale_tensor, m, n, k, b_stride, split_k, ...)`` -
+    projects/skinny_gemm/skinny_gemm_caller.cu:20-340
+  - ``HFRK_skinny_gemm(world_size).skinny_gemm_torch_binding(...)`` -
+    projects/skinny_gemm/skinny_gemm_binding.cu:64-100
+Differences, all forced by the target: bytes are OCP e4m3fn (the reference's
+are AMD e4m3 FNUZ), D is bf16 (reference: fp16) and is overwritten rather than
+accumulated into, and a second per-tensor scale exists (``scale_b``; the
+reference-named wrappers pass 1).
+"""
+from __future__ import annotations
+
+import enum
+
+import torch
+
+from ._lib import check, lib
+
+
+class SkinnyGemmReturnCode(enum.IntEnum):
+    """projects/skinny_gemm/skinny_gemm_caller.cu:9-17, extended."""
+    SUCCESS = 0
+    M_ABOVE_WARPTILE_M = 1
+    N_NOT_EVEN = 2
+    K_NOT_DIVISIBLE_BY_WARPTILE_K = 3
+    TOO_MANY_WARPS = 4
+    QSIZE_TOO_SMALL = 5
+    INVALID_CONFIG = 6
+    BAD_ALIGNMENT = 7
+    BAD_SHAPE = 8
+    CUDA_ERROR = 9
+    DEVICE_TIMEOUT = 10
+    SIZE_ABOVE_LIMIT = 11
+
+
+_ones: dict[int, torch.Tensor] = {}
+
+
+def _one(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _ones:
+        _ones[idx] = torch.ones(1, dtype=torch.float32, device=device)
+    return _ones[idx]
+
+
+def _stream_ptr(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _u8(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dtype == torch.uint8 else t.view(torch.uint8)
+
+
+def skinny_gemm_fp8(A: torch.Tensor, B: torch.Tensor, scale_a: torch.Tensor, scale_b: torch.Tensor,
+                    out: torch.Tensor | None = None) -> torch.Tensor:
+    """D[M,N] = bf16((A . B^T) * scale_a * scale_b) on the current stream.
+
+    A: [M,K] e4m3fn bytes (uint8 or float8_e4m3fn), M <= 32, contiguous.
+    B: [N,K] e4m3fn bytes, K-contiguous (any row pitch that is a multiple of 16).
+    scale_a, scale_b: one fp32 each, on the device.
+    """
+    assert A.is_cuda and B.is_cuda, "device tensors required (there is no CPU path)"
+    A = _u8(A)
+    B = _u8(B)
+    M, K = A.shape
+    N = B.shape[0]
+    assert B.shape[1] == K and B.stride(1) == 1 and A.is_contiguous()
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape == (M, N)
+    with torch.cuda.device(A.device):
+        code = lib().rdb_skinny_gemm_fp8(A.data_ptr(), B.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(),
+                                         out.data_ptr(), M, N, K, B.stride(0), _stream_ptr(A.device))
+    check(code, "rdb_skinny_gemm_fp8")
+    return out
+
+
+def skinny_gemm_fastpath(A, B, D, scale_tensor, m: int, n: int, k: int) -> int:
+    """Reference-named launcher: returns the status code instead of raising.
+
+    Tensors may be torch CUDA tensors or raw device addresses (ints).
+    """
+    ptr = lambda t: t if isinstance(t, int) else t.data_ptr()  # noqa: E731
+    dev = next((t.device for t in (A, B, D) if isinstance(t, torch.Tensor)), torch.device("cuda"))
+    with torch.cuda.device(dev):
+        return int(lib().rdb_skinny_gemm_fp8(ptr(A), ptr(B), ptr(scale_tensor), _one(torch.device(dev)).data_ptr(),
+                                             ptr(D), m, n, k, k, 0))
+
+
+def skinny_gemm(A, B, D, scale_tensor, m, n, k, b_stride, split_k, A_producers, B_producers, consumers,
+                b_lanes, qsize, op_m, ops, stream=None) -> int:
+    """Reference-named full launcher; tuning ints are validated like the
+    reference does and used as hints (split_k, qsize) or ignored."""
+    ptr = lambda t: t if isinstance(t, int) else t.data_ptr()  # noqa: E731
+    dev = next((t.device for t in (A, B, D) if isinstance(t, torch.Tensor)), torch.device("cuda"))
+    with torch.cuda.device(dev):
+        s = _stream_ptr(dev) if stream is None else (stream if isinstance(stream, int) else stream.cuda_stream)
+        return int(lib().rdb_skinny_gemm_fp8_hinted(
+            ptr(A), ptr(B), ptr(scale_tensor), _one(torch.device(dev)).data_ptr(), ptr(D), m, n, k, b_stride,
+            split_k, A_producers, B_producers, consumers, b_lanes, qsize, op_m, ops, s))
+
+
+class HFRK_skinny_gemm:
+    """Mirror of the pybind class of projects/skinny_gemm/skinny_gemm_binding.cu."""
+
+    def __init__(self, world_size: int):
+        self.world_size = int(world_size)
+
+    def skinny_gemm_torch_binding(self, A, B, D, scale_tensor, split_k, A_producers, B_producers, consumers,
+                                  b_lanes, qsize, ops) -> int:
+        # B arrives as a [K,N] view of [N,K] K-contiguous storage; stride(1) is
+        # the row pitch (skinny_gemm_binding.cu:36-39).
+        m, k = A.size(0), A.size(1)
+        n = B.size(1)
+        b_stride = B.stride(1)
+        op_m = 8 if m <= 8 else (16 if m <= 16 else 32)
+        return skinny_gemm(_u8(A), _u8(B), D, scale_tensor, m, n, k, b_stride, split_k, A_producers, B_producers,
+                           consumers, b_lanes, qsize, op_m, ops)
+
+
+class _HostStaging:
+    """Device buffers reused by the host-buffer entry (allocated once per shape)."""
+
+    def __init__(self):
+        self.bufs: dict[tuple, torch.Tensor] = {}
+
+    def get(self, tag: str, shape, dtype, device) -> torch.Tensor:
+        key = (tag, tuple(shape), dtype, str(device))
+        if key not in self.bufs:
+            self.bufs[key] = torch.empty(shape, dtype=dtype, device=device)
+        return self.bufs[key]
+
+
+_staging = _HostStaging()
+
+
+def skinny_gemm_fp8_host(A: torch.Tensor, B: torch.Tensor, scale_a: torch.Tensor, scale_b: torch.Tensor,
+                         out: torch.Tensor, device="cuda") -> torch.Tensor:
+    """Same contraction with HOST (ideally pinned) tensors: copies every input
+    to the device, runs the kernel and copies the bf16 result back into
+    ``out``; everything is queued on the current stream and the call returns
+    after the result has arrived."""
+    dev = torch.device(device)
+    dA = _staging.get("A", A.shape, torch.uint8, dev)
+    dB = _staging.get("B", B.shape, torch.uint8, dev)
+    dsa = _staging.get("sa", (1,), torch.float32, dev)
+    dsb = _staging.get("sb", (1,), torch.float32, dev)
+    dD = _staging.get("D", out.shape, torch.bfloat16, dev)
+    dA.copy_(_u8(A), non_blocking=True)
+    dB.copy_(_u8(B), non_blocking=True)
+    dsa.copy_(scale_a, non_blocking=True)
+    dsb.copy_(scale_b, non_blocking=True)
+    skinny_gemm_fp8(dA, dB, dsa, dsb, out=dD)
+    out.copy_(dD, non_blocking=True)
+    torch.cuda.current_stream(dev).synchronize()
+    return out
