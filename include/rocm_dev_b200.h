@@ -78,6 +78,41 @@ int rdb_skinny_gemm_fp8_hinted(const uint8_t *A, const uint8_t *B, const float *
                                int B_producers, int consumers, int b_lanes, int qsize, int op_m, int ops,
                                void *stream);
 
+/* Tuner entry: the same contraction with the kernel's own knobs exposed.
+ * rows_per_tile (multiple of 16, <= 256), split_k (1..8) and stages select
+ * the tiling; 0 means automatic.  The reference tunes by rewriting #defines
+ * and recompiling (grid.py:106-116 and projects/skinny_gemm/core.cu:29-38);
+ * here the knobs are run-time arguments.
+ * flags: RDB_SKINNY_OVERLAP_PRIOR_KERNEL launches with programmatic stream
+ * serialization: the kernel starts (and prefetches WEIGHTS) while the
+ * preceding kernel of the stream is still finishing, and waits for it only
+ * before it reads A or writes D.  Only valid when B is not written by that
+ * preceding kernel. */
+#define RDB_SKINNY_OVERLAP_PRIOR_KERNEL 1u
+int rdb_skinny_gemm_fp8_tuned(const uint8_t *A, const uint8_t *B, const float *scale_a, const float *scale_b,
+                              uint16_t *D, int M, int N, int K, int ldb, int rows_per_tile, int split_k,
+                              int stages, unsigned flags, void *stream);
+
+/* The tiling the automatic plan picks for a shape on a device with sm_count
+ * SMs (pure host arithmetic, no GPU needed).  Counterpart of the compile-time
+ * knobs of projects/skinny_gemm/core.cu:29-38. */
+int rdb_skinny_gemm_plan(int M, int N, int K, int sm_count, int *rows_per_tile, int *split_k, int *stages);
+
+/* Number of clusters of cluster_size skinny-GEMM CTAs, each with smem_bytes of
+ * dynamic shared memory, that the current device can hold at once (the
+ * planner keeps every launch inside one such wave); -1 on error.  The
+ * reference sizes its grid from a constant instead
+ * (projects/skinny_gemm/core.cu:26, skinny_gemm_caller.cu:78). */
+int rdb_skinny_gemm_max_clusters(int M, int cluster_size, int smem_bytes);
+
+/* Diagnostics (the reference's counterpart is reading the saved ISA,
+ * class_project.py:56-61): registers a device buffer of slots x ctas_per_slot
+ * x 12 uint64.  While registered, skinny launch i writes %globaltimer stamps of
+ * each CTA (entry, set-up done, prior kernel done, first/last stage full,
+ * accumulator done, partials exchanged, exit, epilogue ready / first TMEM load / stores issued) into slot i % slots.  NULL
+ * switches tracing off.  Not thread-safe; leave off in production. */
+int rdb_skinny_gemm_trace(unsigned long long *device_buffer, int slots, int ctas_per_slot);
+
 #ifdef __cplusplus
 }
 #endif

@@ -5,10 +5,12 @@ Host-side mirror of the reference project's launcher interface over a C ABI
 """
 from ._lib import LibraryMissing, RdbError, lib, status_string  # noqa: F401
 from .skinny_gemm import (  # noqa: F401
+    OVERLAP_PRIOR_KERNEL,
     HFRK_skinny_gemm,
     SkinnyGemmReturnCode,
     skinny_gemm,
     skinny_gemm_fastpath,
     skinny_gemm_fp8,
     skinny_gemm_fp8_host,
+    skinny_gemm_fp8_tuned,
 )

@@ -23,6 +23,10 @@ _SIGNATURES = {
     "rdb_version": (C.c_char_p, []),
     "rdb_skinny_gemm_fp8": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, vp]),
     "rdb_skinny_gemm_fp8_hinted": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, i, i, i, i, i, i, i, i, vp]),
+    "rdb_skinny_gemm_plan": (i, [i, i, i, i, vp, vp, vp]),
+    "rdb_skinny_gemm_max_clusters": (i, [i, i, i]),
+    "rdb_skinny_gemm_trace": (i, [vp, i, i]),
+    "rdb_skinny_gemm_fp8_tuned": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, i, i, i, C.c_uint, vp]),
 }
 
 

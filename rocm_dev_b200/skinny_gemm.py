@@ -79,6 +79,22 @@ def skinny_gemm_fp8(A: torch.Tensor, B: torch.Tensor, scale_a: torch.Tensor, sca
     return out
 
 
+OVERLAP_PRIOR_KERNEL = 1
+
+
+def skinny_gemm_fp8_tuned(A, B, scale_a, scale_b, out, rows_per_tile=0, split_k=0, stages=0, flags=0) -> int:
+    """Tuner entry (rdb_skinny_gemm_fp8_tuned): explicit tile height, K split,
+    stage count and launch flags; returns the status code."""
+    A = _u8(A)
+    B = _u8(B)
+    M, K = A.shape
+    N = B.shape[0]
+    with torch.cuda.device(A.device):
+        return int(lib().rdb_skinny_gemm_fp8_tuned(A.data_ptr(), B.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(),
+                                                   out.data_ptr(), M, N, K, B.stride(0), rows_per_tile, split_k,
+                                                   stages, flags, _stream_ptr(A.device)))
+
+
 def skinny_gemm_fastpath(A, B, D, scale_tensor, m: int, n: int, k: int) -> int:
     """Reference-named launcher: returns the status code instead of raising.
 
