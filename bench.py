@@ -30,6 +30,9 @@ sys.path.insert(0, ROOT)
 SHAPES = [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 28672, 4096), ("down", 4096, 14336)]
 MS = [1, 2, 4, 8, 16]
 WEIGHT_SETS = 2
+# DRAM bytes (read + write) per algorithmic byte from the ncu capture summarised in
+# profiles/skinny_gemm_gate_up_M8_full.md (121.5 MB moved for 117.9 MB algorithmic); traffic scales with the bytes.
+TRAFFIC_PER_ALGO_BYTE = 1.03
 METRIC = "skinny FP8 GEMM HBM GB/s, decode sweep M=1..16 over Llama-3-8B-shaped (N,K)"
 
 
@@ -235,11 +238,13 @@ def run_gpu(args):
             sampler.start()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.profiler.start()          # lets `ncu --profile-from-start off` see only the timed region
         e0.record(stream)
         for s in range(args.steps):
             graphs[s % 2].replay()
         e1.record(stream)
         torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
         if world > 1:
             dist.barrier()
         clocks = sampler.stop() if rank == 0 else None
@@ -343,7 +348,7 @@ def run_gpu(args):
                          "only after 436 MB of other weights", "launch": "CUDA graph, programmatic dependent launch",
                    "multi_gpu": "replicas only"},
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
-                     "traffic": None, "peak_kind": f"of {peak_kind}", "kernel": "skinny_gemm_kernel",
+                     "traffic": TRAFFIC_PER_ALGO_BYTE * step_bytes() / launches_per_step, "peak_kind": f"of {peak_kind}", "kernel": "skinny_gemm_kernel",
                      "algorithmic_bytes_per_launch": step_bytes() / launches_per_step,
                      "avg_launch_us": ms * 1e3 / (args.steps * launches_per_step)},
         "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
