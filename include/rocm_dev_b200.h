@@ -113,6 +113,23 @@ int rdb_skinny_gemm_max_clusters(int M, int cluster_size, int smem_bytes);
  * switches tracing off.  Not thread-safe; leave off in production. */
 int rdb_skinny_gemm_trace(unsigned long long *device_buffer, int slots, int ctas_per_slot);
 
+/* -------------------------------------------------------------- dense GEMM
+ * D[M,N] = bf16( (A . B^T) * scale_a[0] * scale_b[0] ), any M, N; K % 16 == 0.
+ *   A [M,K] and B [N,K] row-major fp8 (K-contiguous), D [M,N] row-major bf16,
+ *   OVERWRITTEN.  One persistent tcgen05 kernel replaces the three
+ *   producer/consumer projects: async_gemm<T> of
+ *   projects/async_gemm_16x16x64/src.cu:54-82,
+ *   projects/async_gemm_blanes/sparse_k.cu:46-80 and
+ *   projects/async_gemm_sparse/sparse_k.cu:45-75 (whose output was unscaled
+ *   fp32 accumulated into a zeroed D, and which exit(1) on a shape that does
+ *   not divide their tile; here any shape is accepted and errors are returned). */
+int rdb_dense_gemm_fp8(const uint8_t *A, const uint8_t *B, const float *scale_a, const float *scale_b,
+                       uint16_t *D, int M, int N, int K, void *stream);
+
+/* The reference's own output convention for the same projects: unscaled fp32,
+ * D [M,N] OVERWRITTEN (async_gemm<float>, same citations). */
+int rdb_dense_gemm_fp8_f32(const uint8_t *A, const uint8_t *B, float *D, int M, int N, int K, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,258 @@
+// Dense FP8 GEMM for sm_100a:  D[M,N] = (A . B^T) [* sa * sb], A [M,K], B [N,K], both e4m3 K-contiguous.
+//
+// One kernel replaces the three producer/consumer GEMM projects of the
+// reference (projects/async_gemm_16x16x64/src.cu:5-82, projects/
+// async_gemm_blanes/sparse_k.cu:5-80, projects/async_gemm_sparse/sparse_k.cu:
+// 5-75 and their producer.cu / consumer.cu), whose 16x16, 16x48 and 8x64 tiles
+// per block re-read the operands from L2 at 16 flop/byte.  Here a persistent
+// CTA per SM walks 128 x 256 output tiles:
+//   warp 0    one thread issues TMA loads (A box 128 x 128 B, B box 256 x 128 B)
+//             into a 4-stage ring guarded by full/empty mbarriers;
+//   warp 1    allocates all 512 TMEM columns (two 128 x 256 fp32 accumulators);
+//             one thread issues tcgen05.mma kind::f8f6f4 (128 x 256 x 32), frees
+//             stages with tcgen05.commit and hands finished accumulators over;
+//   warps 2-5 epilogue: tcgen05.ld the accumulator (one row per thread), scale,
+//             convert and store while the next tile's MMAs fill the other
+//             accumulator.
+// The "B lanes" of async_gemm_blanes (one A tile feeding several B tiles) are
+// simply the wide UMMA N; split-K and its fp32 atomics are gone, D is
+// overwritten.  Tiles are ordered in groups of 16 tile-rows so that the ~148
+// tiles in flight share operand panels in L2.
+#include <cuda_bf16.h>
+
+#include "host_util.h"
+#include "ptx.cuh"
+
+namespace rdb {
+namespace dense {
+
+constexpr int BM = 128, BN = 256, BK = 128;
+constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
+constexpr int STAGES = 4;
+constexpr int NUM_THREADS = 192;
+constexpr int GROUP_M = 16;
+constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+
+struct Params {
+    void* D;
+    const float* scale_a;   // nullptr: unscaled
+    const float* scale_b;
+    int* status;
+    int M, N, num_kb, tiles_m, tiles_n;
+    int out_f32;            // 1: fp32 output, 0: bf16
+};
+
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& mb, int& nb) {
+    const int per_group = GROUP_M * tiles_n;
+    const int g = tile / per_group, r = tile - g * per_group;
+    const int first = g * GROUP_M;
+    const int gsize = tiles_m - first < GROUP_M ? tiles_m - first : GROUP_M;
+    mb = first + r % gsize;
+    nb = r / gsize;
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+dense_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + STAGES);
+    const uint32_t acc_full0 = smem_u32(bars + 2 * STAGES), acc_empty0 = smem_u32(bars + 2 * STAGES + 2);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t stage0 = smem_u32(smem);
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmA);
+        prefetch_tensormap(&tmB);
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(acc_full0 + 8 * a, 1);
+            mbar_init(acc_empty0 + 8 * a, 4);   // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    const int num_tiles = p.tiles_m * p.tiles_n;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint64_t pol = l2_policy_evict_last();   // operand panels are re-read by neighbouring tiles
+            int it = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && *abort_flag == 0; tile += gridDim.x) {
+                int mb, nb;
+                tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+                for (int kb = 0; kb < p.num_kb; kb++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { *abort_flag = 1; report_timeout(p.status); break; }
+                    const uint32_t dst = stage0 + s * STAGE_BYTES;
+                    mbar_arrive_expect_tx(full0 + 8 * s, STAGE_BYTES);
+                    tma_load_2d(dst, &tmA, kb * BK, mb * BM, full0 + 8 * s, pol);
+                    tma_load_2d(dst + A_BYTES, &tmB, kb * BK, nb * BN, full0 + 8 * s, pol);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = idesc_e4m3_f32(BM, BN);
+            int it = 0, t = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && *abort_flag == 0; tile += gridDim.x, t++) {
+                const int acc = t & 1;
+                // the epilogue must have drained this accumulator (two tiles ago)
+                if (!mbar_wait(acc_empty0 + 8 * acc, ((t >> 1) & 1) ^ 1)) { *abort_flag = 1; report_timeout(p.status); break; }
+                tc_fence_after_sync();
+                const uint32_t d = tmem_base + acc * BN;
+                for (int kb = 0; kb < p.num_kb; kb++, it++) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(full0 + 8 * s, ph)) { *abort_flag = 1; report_timeout(p.status); break; }
+                    tc_fence_after_sync();
+                    const uint32_t a = stage0 + s * STAGE_BYTES, b = a + A_BYTES;
+#pragma unroll
+                    for (int ks = 0; ks < BK / 32; ks++)
+                        tc_mma_f8(d, smem_desc_k128(a + ks * 32), smem_desc_k128(b + ks * 32), idesc, (kb | ks) != 0);
+                    tc_commit(empty0 + 8 * s);
+                }
+                tc_commit(acc_full0 + 8 * acc);
+            }
+        }
+        __syncwarp();
+    } else {
+        // epilogue warps: TMEM lane quadrant = warp % 4, one output row per thread
+        const int quad = warp & 3;
+        float sc = 1.0f;
+        if (p.scale_a) sc = __ldg(p.scale_a) * __ldg(p.scale_b);
+        const bool vec8 = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
+        int t = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, t++) {
+            int mb, nb;
+            tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
+            const int acc = t & 1;
+            bool ok = mbar_wait(acc_full0 + 8 * acc, (t >> 1) & 1);
+            if (!ok) { *abort_flag = 1; report_timeout(p.status); }
+            if (*abort_flag != 0) break;
+            tc_fence_after_sync();
+            const int row = mb * BM + quad * 32 + lane;
+            const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                float v[32];
+                tmem_ld32(taddr + c0, v);
+                const int col = nb * BN + c0;
+                if (row < p.M && col < p.N) {
+                    if (p.out_f32) {
+                        float* out = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.N + col;
+                        if (p.N % 4 == 0 && col + 31 < p.N) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(out + j) = make_float4(v[j] * sc, v[j + 1] * sc, v[j + 2] * sc, v[j + 3] * sc);
+                        } else {
+                            for (int j = 0; j < 32; j++)
+                                if (col + j < p.N) out[j] = v[j] * sc;
+                        }
+                    } else {
+                        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.N + col;
+                        if (vec8 && col + 31 < p.N) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                __nv_bfloat162 b0 = __floats2bfloat162_rn(v[j] * sc, v[j + 1] * sc), b1 = __floats2bfloat162_rn(v[j + 2] * sc, v[j + 3] * sc);
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(v[j + 4] * sc, v[j + 5] * sc), b3 = __floats2bfloat162_rn(v[j + 6] * sc, v[j + 7] * sc);
+                                uint4 o;
+                                o.x = *reinterpret_cast<uint32_t*>(&b0); o.y = *reinterpret_cast<uint32_t*>(&b1);
+                                o.z = *reinterpret_cast<uint32_t*>(&b2); o.w = *reinterpret_cast<uint32_t*>(&b3);
+                                *reinterpret_cast<uint4*>(out + j) = o;
+                            }
+                        } else {
+                            for (int j = 0; j < 32; j++)
+                                if (col + j < p.N) out[j] = __float2bfloat16_rn(v[j] * sc);
+                        }
+                    }
+                }
+            }
+            // all of this warp's TMEM reads are complete: hand the accumulator back
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty0 + 8 * acc);
+        }
+    }
+
+    if (*abort_flag != 0) {
+        for (int i = 0; i < 64; i++) __nanosleep(2000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+static int run(const uint8_t* A, const uint8_t* B, const float* sa, const float* sb, void* D, int out_f32, int M, int N,
+               int K, int max_ctas, cudaStream_t stream) {
+    if (M < 1 || N < 1 || K < 1) return RDB_BAD_SHAPE;
+    if (K % 16 != 0) return RDB_K_NOT_DIVISIBLE_BY_WARPTILE_K;
+    if (!aligned16(A) || !aligned16(B) || (reinterpret_cast<uintptr_t>(D) & 3u)) return RDB_BAD_ALIGNMENT;
+    if ((sa == nullptr) != (sb == nullptr)) return RDB_INVALID_CONFIG;
+    int err = 0;
+    DeviceInfo* info = device_info(&err);
+    if (!info) return err;
+    static bool attr_set[kMaxDevices] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev]) {
+        if (cudaFuncSetAttribute(dense_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+            return RDB_CUDA_ERROR;
+        attr_set[dev] = true;
+    }
+    CUtensorMap tmA, tmB;
+    int r = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != RDB_SUCCESS) return r;
+    r = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != RDB_SUCCESS) return r;
+    Params p;
+    p.D = D;
+    p.scale_a = sa;
+    p.scale_b = sb;
+    p.status = info->status_dev;
+    p.M = M;
+    p.N = N;
+    p.num_kb = (K + BK - 1) / BK;
+    p.tiles_m = (M + BM - 1) / BM;
+    p.tiles_n = (N + BN - 1) / BN;
+    p.out_f32 = out_f32;
+    int grid = p.tiles_m * p.tiles_n;
+    int cap = info->sm_count;
+    if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
+    if (grid > cap) grid = cap;
+    dense_gemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+    return cudaGetLastError() == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
+}
+
+}  // namespace dense
+}  // namespace rdb
+
+extern "C" {
+
+int rdb_dense_gemm_fp8(const uint8_t* A, const uint8_t* B, const float* scale_a, const float* scale_b, uint16_t* D,
+                       int M, int N, int K, void* stream) {
+    if (!scale_a || !scale_b) return RDB_INVALID_CONFIG;
+    return rdb::dense::run(A, B, scale_a, scale_b, D, 0, M, N, K, 0, static_cast<cudaStream_t>(stream));
+}
+
+int rdb_dense_gemm_fp8_f32(const uint8_t* A, const uint8_t* B, float* D, int M, int N, int K, void* stream) {
+    return rdb::dense::run(A, B, nullptr, nullptr, D, 1, M, N, K, 0, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

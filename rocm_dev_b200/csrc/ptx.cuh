@@ -62,13 +62,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // Wait budget of every bounded wait, in nanoseconds of %globaltimer.
 constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;
 
-// Bounded phase wait.  Returns false when the budget ran out.
+// Bounded phase wait.  Returns false when the budget ran out.  %globaltimer is
+// slow to read (a read per wait capped a TMA pipeline at one box per ~260 ns),
+// so the common case spins on try_wait alone - each try_wait already suspends
+// the thread for a hardware-defined interval - and the timer is consulted only
+// after many failed polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
-    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 2048; i++)
+        if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0xFF) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) return false;
+        if ((++spins & 0x3FF) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) return false;
     }
     return true;
 }
