@@ -130,6 +130,28 @@ int rdb_dense_gemm_fp8(const uint8_t *A, const uint8_t *B, const float *scale_a,
  * D [M,N] OVERWRITTEN (async_gemm<float>, same citations). */
 int rdb_dense_gemm_fp8_f32(const uint8_t *A, const uint8_t *B, float *D, int M, int N, int K, void *stream);
 
+/* ---------------------------------------------------------- sum reduce
+ * D[m,n] = sum over the batch of (A[i,m,n] + B[i,m,n]), fp32, summed in batch
+ * order (bit-identical to the host loop).  A, B [b,m,n], D [m,n], any m, n;
+ * b = 0 writes zeros.  Replaces tiled_sum_reduce(A, B, D, b, m, n) of
+ * projects/tiled_sum_reduce/src.cu:52-73 and projects/tiled_sum_reduce_async/
+ * src.cu:179-200 (which only warn when m % 8 or n % 64 is non-zero). */
+int rdb_tiled_sum_reduce(const float *A, const float *B, float *D, int b, int m, int n, void *stream);
+
+/* ---------------------------------------------------------- grid barrier
+ * The reference's barrier probe, globs(uint* D) of projects/global_sync/
+ * src.cu:15-27: 2 blocks x 64 threads write D[block] = 0, meet at a grid-wide
+ * barrier, then atomicDec D[block].  D needs one word per block.  The barrier
+ * is a bounded counter barrier (RDB_DEVICE_TIMEOUT in the status word if it
+ * runs out); its two counter words live in a per-device allocation made on the
+ * first call. */
+int rdb_globs(uint32_t *D, void *stream);
+
+/* The same probe with `blocks` x `threads` and the write/barrier/decrement body
+ * repeated `rounds` times (barrier latency at full-grid size).  blocks must be
+ * co-resident (cooperative launch). */
+int rdb_globs_n(uint32_t *D, int blocks, int threads, int rounds, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

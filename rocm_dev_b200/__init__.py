@@ -5,6 +5,7 @@ Host-side mirror of the reference project's launcher interface over a C ABI
 """
 from ._lib import LibraryMissing, RdbError, lib, status_string  # noqa: F401
 from .async_gemm import AsyncGemmShapeError, async_gemm, dense_gemm_fp8  # noqa: F401
+from .reduce import globs, globs_n, tiled_sum_reduce  # noqa: F401
 from .skinny_gemm import (  # noqa: F401
     OVERLAP_PRIOR_KERNEL,
     HFRK_skinny_gemm,
