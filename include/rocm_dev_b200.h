@@ -152,6 +152,30 @@ int rdb_globs(uint32_t *D, void *stream);
  * co-resident (cooperative launch). */
 int rdb_globs_n(uint32_t *D, int blocks, int threads, int rounds, void *stream);
 
+/* rdb_globs_n for callers that must not allocate device memory while they
+ * run - a host application that owns all GPU memory and gives its plugins a
+ * fixed arena, or a latency-critical loop where a device allocation (it
+ * synchronises the whole GPU) cannot be tolerated.  This entry point has no
+ * counterpart in the reference.  It never calls cudaMalloc / cudaFree or any
+ * other allocating routine: the two barrier counters and a status word live in
+ * a 256-byte array compiled into the library (each GPU that loads the library
+ * holds it until the process exits).  The caller still passes D.
+ *   - Limit: at most 1024 blocks and blocks x rounds <= 2^30; anything larger
+ *     returns RDB_SIZE_ABOVE_LIMIT and prints the reason on stderr.
+ *   - The first call on each device looks up the array's device address; make
+ *     that first call before starting any stream capture.
+ *   - All calls on one GPU share the array.  The counters are cleared (on
+ *     `stream`) before every launch, so a call is independent of what the
+ *     previous one left behind; two calls whose kernels overlap on the GPU
+ *     (different streams) race on the counters - serialise them.
+ *   - A timed-out barrier is reported through rdb_noalloc_status(), not
+ *     through rdb_device_status(). */
+int rdb_globs_n_noalloc(uint32_t *D, int blocks, int threads, int rounds, void *stream);
+
+/* Synchronises the current device and returns (and clears) the status word of
+ * the built-in scratch: RDB_SUCCESS or RDB_DEVICE_TIMEOUT.  Allocates nothing. */
+int rdb_noalloc_status(void);
+
 #ifdef __cplusplus
 }
 #endif

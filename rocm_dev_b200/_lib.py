@@ -32,6 +32,8 @@ _SIGNATURES = {
     "rdb_tiled_sum_reduce": (i, [vp, vp, vp, i, i, i, vp]),
     "rdb_globs": (i, [vp, vp]),
     "rdb_globs_n": (i, [vp, i, i, i, vp]),
+    "rdb_globs_n_noalloc": (i, [vp, i, i, i, vp]),
+    "rdb_noalloc_status": (i, []),
 }
 
 

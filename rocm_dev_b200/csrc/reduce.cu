@@ -16,6 +16,7 @@
 // bounded one of sync.cuh instead of cooperative_groups::this_grid().sync().
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <mutex>
 
 #include "host_util.h"
@@ -115,6 +116,41 @@ int launch_globs(unsigned* D, unsigned* words, int blocks, int threads, int roun
     return e == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
 }
 
+// ------------------------------------------------ allocation-free variant
+// The barrier words of the probe normally sit in a buffer the library
+// allocates on first use.  Some callers may not allocate at all once they are
+// running: a host framework that owns every byte of device memory and hands
+// plugins a fixed arena, or a latency-critical loop in which a device
+// allocation (which synchronises the whole GPU) is unacceptable.  For them the
+// same kernel can run on words that live in this file-scope array instead.
+// Every GPU that loads the library holds these 256 bytes until the process
+// exits.  Word 0/1: barrier arrivals / departures, word 2: status, rest unused.
+constexpr int kNoAllocWords = 64;
+constexpr int kNoAllocMaxBlocks = 1024;
+constexpr long long kNoAllocMaxArrivals = 1ll << 30;   // the arrival word counts blocks x rounds per launch
+static __device__ __align__(256) unsigned g_noalloc_scratch[kNoAllocWords];
+
+// In host code `g_noalloc_scratch` is only a handle for the runtime, not a
+// device address, so the address is looked up once per device (with that
+// device current) and cached.  Nothing is allocated here.
+static unsigned* noalloc_scratch(int* err) {
+    static unsigned* ptr[kMaxDevices] = {};
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { *err = RDB_CUDA_ERROR; return nullptr; }
+    std::lock_guard<std::mutex> lk(mu);
+    if (!ptr[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || p == nullptr) {
+            cudaGetLastError();
+            *err = RDB_CUDA_ERROR;
+            return nullptr;
+        }
+        ptr[dev] = static_cast<unsigned*>(p);
+    }
+    return ptr[dev];
+}
+
 }  // namespace reduce
 }  // namespace rdb
 
@@ -153,5 +189,36 @@ int rdb_globs_n(uint32_t* D, int blocks, int threads, int rounds, void* stream) 
 }
 
 int rdb_globs(uint32_t* D, void* stream) { return rdb_globs_n(D, 2, 64, 1, stream); }
+
+int rdb_globs_n_noalloc(uint32_t* D, int blocks, int threads, int rounds, void* stream) {
+    using namespace rdb::reduce;
+    if (blocks < 1 || threads < 1 || threads > 1024 || rounds < 1) return RDB_BAD_SHAPE;
+    if (blocks > kNoAllocMaxBlocks || static_cast<long long>(blocks) * rounds > kNoAllocMaxArrivals) {
+        fprintf(stderr,
+                "rdb_globs_n_noalloc: %d blocks x %d rounds is beyond what the built-in scratch supports "
+                "(at most %d blocks and %lld barrier arrivals per launch)\n",
+                blocks, rounds, kNoAllocMaxBlocks, kNoAllocMaxArrivals);
+        return RDB_SIZE_ABOVE_LIMIT;
+    }
+    int err = 0;
+    unsigned* words = noalloc_scratch(&err);
+    if (!words) return err;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // The array keeps whatever the previous call left (a timed-out barrier leaves
+    // its counters mid-count): the two barrier words must start at zero.
+    if (cudaMemsetAsync(words, 0, 2 * sizeof(unsigned), s) != cudaSuccess) return RDB_CUDA_ERROR;
+    return launch_globs(D, words, blocks, threads, rounds, reinterpret_cast<int*>(words + 2), s);
+}
+
+int rdb_noalloc_status(void) {
+    int err = 0;
+    unsigned* words = rdb::reduce::noalloc_scratch(&err);
+    if (!words) return err;
+    if (cudaDeviceSynchronize() != cudaSuccess) return RDB_CUDA_ERROR;
+    int st = 0;
+    if (cudaMemcpy(&st, words + 2, sizeof(int), cudaMemcpyDeviceToHost) != cudaSuccess) return RDB_CUDA_ERROR;
+    if (st != 0 && cudaMemset(words + 2, 0, sizeof(int)) != cudaSuccess) return RDB_CUDA_ERROR;
+    return st;
+}
 
 }  // extern "C"
