@@ -152,6 +152,51 @@ int rdb_globs(uint32_t *D, void *stream);
  * co-resident (cooperative launch). */
 int rdb_globs_n(uint32_t *D, int blocks, int threads, int rounds, void *stream);
 
+/* ------------------------------------------------ FP8-encoded allreduce
+ * out[i] = bf16( sum over ranks r = 0..world-1, in rank order, of
+ * fp32(q_r[i]) * s_r[i / 128] ), where (q_r, s_r) encodes rank r's bf16 vector
+ * in blocks of 128: s = amax/448 (1 for an all-zero block), q =
+ * e4m3fn_sat_rn(x / s).  Identical bits on every rank.  One process per GPU;
+ * encoded blocks travel as stores into peer memory over NVLink.  The reference
+ * names this path (an FP8 allreduce over mscclpp) but contains no code for it,
+ * so there is no reference interface to cite; tiled_sum_reduce
+ * (projects/tiled_sum_reduce/src.cu:52-73) is its local reduction step.
+ *
+ * Set-up, once per rank: size a workspace, allocate it (it must come from
+ * rdb_ar_workspace_alloc so that it can be exported), export its 64-byte IPC
+ * handle, exchange handles between the processes, import the peers', then
+ * create the context with the `world` workspace pointers in rank order (the
+ * own one at index `rank`). */
+size_t rdb_ar_workspace_bytes(int world, size_t max_elems);
+int rdb_ar_workspace_alloc(size_t bytes, void **ptr);
+int rdb_ar_workspace_free(void *ptr);
+int rdb_ar_ipc_export(void *ptr, uint8_t *handle64);
+int rdb_ar_ipc_import(const uint8_t *handle64, void **ptr);
+int rdb_ar_ipc_close(void *ptr);
+int rdb_ar_create(int rank, int world, void *const *workspaces, size_t max_elems, void **ctx);
+int rdb_ar_destroy(void *ctx);
+
+/* Collective: every rank calls it with the same n (a multiple of 128, at most
+ * max_elems) and algo (0 automatic, 1 one-shot: every rank receives and
+ * reduces everything, n <= 2^20; 2 two-shot: FP8 reduce-scatter then bf16
+ * all-gather).  x, out: device pointers to n bf16.  out may be NULL for the
+ * two-shot algorithm: the result then stays in the workspace (rdb_ar_result)
+ * until this rank's next call. */
+int rdb_ar_allreduce(void *ctx, const uint16_t *x, uint16_t *out, size_t n, int algo, void *stream);
+const uint16_t *rdb_ar_result(void *ctx);
+
+/* The three launches of a call one by one (phase 1 push, 2 reduce, 3 gather),
+ * all with the epoch rdb_ar_begin_call returned.  For drivers that emulate
+ * several ranks on ONE GPU: issue phase p for every rank before phase p+1 for
+ * any, so that no launch waits for one that has not been issued. */
+int rdb_ar_begin_call(void *ctx);
+int rdb_ar_phase(void *ctx, int phase, int epoch, const uint16_t *x, uint16_t *out, size_t n, int algo,
+                 void *stream);
+
+/* The encoding step alone: q [n] e4m3fn bytes and scales [n/128] of a bf16
+ * vector (n a multiple of 128), bit-exact with the definition above. */
+int rdb_quantize_blocks128(const uint16_t *x, uint8_t *q, float *scales, size_t n, void *stream);
+
 /* rdb_globs_n for callers that must not allocate device memory while they
  * run - a host application that owns all GPU memory and gives its plugins a
  * fixed arena, or a latency-critical loop where a device allocation (it

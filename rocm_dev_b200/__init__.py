@@ -4,6 +4,7 @@ Host-side mirror of the reference project's launcher interface over a C ABI
 (include/rocm_dev_b200.h).  PyTorch is used for device memory and streams only.
 """
 from ._lib import LibraryMissing, RdbError, lib, status_string  # noqa: F401
+from .allreduce import Fp8AllReduce, LocalRanks, quantize_blocks128, shard_groups  # noqa: F401
 from .async_gemm import AsyncGemmShapeError, async_gemm, dense_gemm_fp8  # noqa: F401
 from .reduce import globs, globs_n, tiled_sum_reduce  # noqa: F401
 from .skinny_gemm import (  # noqa: F401

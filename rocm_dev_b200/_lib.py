@@ -32,6 +32,19 @@ _SIGNATURES = {
     "rdb_tiled_sum_reduce": (i, [vp, vp, vp, i, i, i, vp]),
     "rdb_globs": (i, [vp, vp]),
     "rdb_globs_n": (i, [vp, i, i, i, vp]),
+    "rdb_ar_workspace_bytes": (C.c_size_t, [i, C.c_size_t]),
+    "rdb_ar_workspace_alloc": (i, [C.c_size_t, C.POINTER(C.c_void_p)]),
+    "rdb_ar_workspace_free": (i, [vp]),
+    "rdb_ar_ipc_export": (i, [vp, C.c_char_p]),
+    "rdb_ar_ipc_import": (i, [C.c_char_p, C.POINTER(C.c_void_p)]),
+    "rdb_ar_ipc_close": (i, [vp]),
+    "rdb_ar_create": (i, [i, i, C.POINTER(C.c_void_p), C.c_size_t, C.POINTER(C.c_void_p)]),
+    "rdb_ar_destroy": (i, [vp]),
+    "rdb_ar_allreduce": (i, [vp, vp, vp, C.c_size_t, i, vp]),
+    "rdb_ar_result": (C.c_void_p, [vp]),
+    "rdb_ar_begin_call": (i, [vp]),
+    "rdb_ar_phase": (i, [vp, i, i, vp, vp, C.c_size_t, i, vp]),
+    "rdb_quantize_blocks128": (i, [vp, vp, vp, C.c_size_t, vp]),
     "rdb_globs_n_noalloc": (i, [vp, i, i, i, vp]),
     "rdb_noalloc_status": (i, []),
 }

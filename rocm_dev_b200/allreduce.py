@@ -1,0 +1,149 @@
+"""Host side of the FP8-encoded allreduce (one process per GPU).
+
+The reference project names this path (an FP8 allreduce over mscclpp) but holds
+no code for it; the semantics are those of the configuration text: per-128
+element e4m3fn blocks with an fp32 scale amax/448, fp32 accumulation in rank
+order, one bf16 rounding, identical bits on every rank.  ``torch.distributed``
+is used only to exchange the 64-byte IPC handles of the workspaces at set-up;
+the data path is the library's own kernels storing into peer memory.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from ._lib import check, lib
+
+GROUP = 512          # elements per unit of ownership (4 blocks of 128)
+ONE_SHOT, TWO_SHOT, AUTO = 1, 2, 0
+
+
+def shard_groups(n: int, world: int):
+    """[(first_group, end_group)] per rank: which 512-element groups of an
+    n-element vector each rank reduces in the two-shot algorithm."""
+    groups = (n + GROUP - 1) // GROUP
+    return [(groups * r // world, groups * (r + 1) // world) for r in range(world)]
+
+
+def quantize_blocks128(x: torch.Tensor):
+    """Device encoder: (q uint8 like x, scales fp32 [numel/128]) of a bf16 tensor."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous() and x.numel() % 128 == 0
+    q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    s = torch.empty(x.numel() // 128, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().rdb_quantize_blocks128(x.data_ptr(), q.data_ptr(), s.data_ptr(), x.numel(),
+                                           torch.cuda.current_stream(x.device).cuda_stream), "rdb_quantize_blocks128")
+    return q, s
+
+
+class _Workspace:
+    def __init__(self, world: int, max_elems: int):
+        self.bytes = int(lib().rdb_ar_workspace_bytes(world, max_elems))
+        if self.bytes == 0:
+            raise ValueError("world must be 1..8 and max_elems positive")
+        p = C.c_void_p()
+        check(lib().rdb_ar_workspace_alloc(self.bytes, C.byref(p)), "rdb_ar_workspace_alloc")
+        self.ptr = p.value
+
+    def handle(self) -> bytes:
+        buf = C.create_string_buffer(64)
+        check(lib().rdb_ar_ipc_export(self.ptr, buf), "rdb_ar_ipc_export")
+        return buf.raw
+
+    def free(self):
+        if self.ptr:
+            lib().rdb_ar_workspace_free(self.ptr)
+            self.ptr = None
+
+
+def _create(rank: int, world: int, ptrs, max_elems: int) -> int:
+    arr = (C.c_void_p * world)(*ptrs)
+    ctx = C.c_void_p()
+    check(lib().rdb_ar_create(rank, world, arr, max_elems, C.byref(ctx)), "rdb_ar_create")
+    return ctx.value
+
+
+class Fp8AllReduce:
+    """Collective object of one rank.  ``all_reduce(x)`` must be called by
+    every rank of the group with tensors of the same size."""
+
+    def __init__(self, max_elems: int, group=None, device=None):
+        import torch.distributed as dist
+        self.group = group
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+        self.max_elems = int(max_elems)
+        with torch.cuda.device(self.device):
+            self.ws = _Workspace(self.world, self.max_elems)
+            handles = [None] * self.world
+            dist.all_gather_object(handles, self.ws.handle(), group=group)
+            self.peers = []
+            ptrs = []
+            for r, h in enumerate(handles):
+                if r == self.rank:
+                    ptrs.append(self.ws.ptr)
+                    continue
+                p = C.c_void_p()
+                check(lib().rdb_ar_ipc_import(h, C.byref(p)), "rdb_ar_ipc_import")
+                self.peers.append(p.value)
+                ptrs.append(p.value)
+            self.ctx = _create(self.rank, self.world, ptrs, self.max_elems)
+        dist.barrier(group=group)
+
+    def all_reduce(self, x: torch.Tensor, out: torch.Tensor | None = None, algo: int = AUTO) -> torch.Tensor:
+        assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
+        n = x.numel()
+        if out is None:
+            out = torch.empty_like(x)
+        assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.numel() == n
+        with torch.cuda.device(self.device):
+            check(lib().rdb_ar_allreduce(self.ctx, x.data_ptr(), out.data_ptr(), n, algo,
+                                         torch.cuda.current_stream(self.device).cuda_stream), "rdb_ar_allreduce")
+        return out
+
+    def close(self):
+        if getattr(self, "ctx", None):
+            torch.cuda.synchronize(self.device)
+            lib().rdb_ar_destroy(self.ctx)
+            self.ctx = None
+            for p in self.peers:
+                lib().rdb_ar_ipc_close(p)
+            self.ws.free()
+
+
+class LocalRanks:
+    """W ranks emulated on ONE GPU (tests and single-GPU drivers): W
+    workspaces on the same device, and each phase issued for every rank before
+    the next phase of any, so that no launch waits on one not yet issued."""
+
+    def __init__(self, world: int, max_elems: int, device="cuda"):
+        self.world, self.device = world, torch.device(device)
+        with torch.cuda.device(self.device):
+            self.ws = [_Workspace(world, max_elems) for _ in range(world)]
+            ptrs = [w.ptr for w in self.ws]
+            self.ctx = [_create(r, world, ptrs, max_elems) for r in range(world)]
+
+    def all_reduce(self, xs, algo: int = AUTO):
+        """xs: list of W bf16 tensors (one per emulated rank) -> list of W results."""
+        n = xs[0].numel()
+        outs = [torch.empty_like(x) for x in xs]
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        with torch.cuda.device(self.device):
+            epochs = {int(lib().rdb_ar_begin_call(c)) for c in self.ctx}
+            assert len(epochs) == 1
+            epoch = epochs.pop()
+            for phase in (1, 2, 3):
+                for r in range(self.world):
+                    check(lib().rdb_ar_phase(self.ctx[r], phase, epoch, xs[r].data_ptr(), outs[r].data_ptr(), n, algo,
+                                             stream), "rdb_ar_phase")
+        return outs
+
+    def close(self):
+        torch.cuda.synchronize(self.device)
+        for c in self.ctx:
+            lib().rdb_ar_destroy(c)
+        for w in self.ws:
+            w.free()
+        self.ctx, self.ws = [], []

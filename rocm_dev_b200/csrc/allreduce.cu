@@ -1,0 +1,475 @@
+// FP8-encoded allreduce over NVLink peer memory (one process per GPU).
+//
+// Semantics (there is no reference code for this path; the definition is the
+// configuration text restated by the CPU oracle): every rank's bf16 vector is
+// encoded in blocks of 128 elements - fp32 scale s = amax/448 (1 for an
+// all-zero block), q = e4m3fn_sat_rn(x / s) - and the result on every rank is
+// bf16_rn( sum over ranks r = 0..W-1, in rank order, of fp32(q_r) * s_r ), the
+// product and the sum rounded separately in fp32.  All ranks produce identical
+// bits.
+//
+// Data path.  Each rank owns a workspace (cudaMalloc'd, exported through CUDA
+// IPC) holding a staging area for incoming encoded blocks, a gather area for
+// the bf16 result and flag words.  A call runs three launches on the caller's
+// stream:
+//   phase 1  quantise the local vector and PUSH the encoded bytes and scales
+//            straight into the staging slot of the rank that owns each
+//            512-element group (two-shot) or of every rank (one-shot, small
+//            messages): coalesced 16-byte remote stores, nothing is staged
+//            locally;
+//            the last block to finish publishes "my pushes are complete" to
+//            every peer (release, system scope);
+//   phase 2  wait (bounded) for every peer's flag, then dequantise the W copies of
+//            the owned groups, accumulate in fp32 in rank order, round once to
+//            bf16 and push the result into every rank's gather area (two-shot)
+//            or write it straight to the output (one-shot);
+//            and publish "my part of the result is delivered";
+//   phase 3  (two-shot) wait for those flags and, if the caller wants the result
+//            in its own buffer, copy it out of the gather area.
+// Flags carry a per-call epoch, so nothing is reset between calls; the staging
+// area has two sets used alternately (epoch parity) because a fast rank may
+// start pushing call e+1 while a slow one still reduces call e.  Loads are
+// never issued against another GPU's memory: all remote traffic is stores.
+// Waits are bounded; a timeout stores RDB_DEVICE_TIMEOUT in the status word.
+//
+// The three phases are separate launches rather than one cooperative kernel so
+// that a single GPU can emulate W ranks legally (all phase-1 launches, then all
+// phase-2 launches, ...): no launch then waits on one that has not been issued.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+
+#include <cstring>
+
+#include "host_util.h"
+#include "ptx.cuh"
+
+namespace rdb {
+namespace ar {
+
+constexpr int kMaxWorld = 8;
+constexpr int kGroup = 512;               // elements per work item: 4 blocks of 128
+constexpr size_t kOneShotMaxElems = 1u << 20;
+constexpr int kThreads = 256;
+
+struct Layout {
+    size_t slot_groups;   // groups one source rank may push into one slot
+    size_t off_q;         // [2][W][slot_groups * 512] bytes   (two sets, used alternately: set = epoch & 1)
+    size_t off_s;         // [2][W][slot_groups * 4] floats
+    size_t off_gather;    // [max_elems] bf16
+    size_t off_flags;     // [2][kMaxWorld] uint32 epochs (+ padding)
+    size_t bytes;
+};
+
+__host__ __device__ inline size_t round_up(size_t x, size_t m) { return (x + m - 1) / m * m; }
+
+static Layout make_layout(int world, size_t max_elems) {
+    Layout L;
+    const size_t groups = (max_elems + kGroup - 1) / kGroup;
+    const size_t shard = (groups + world - 1) / world;
+    const size_t one = (kOneShotMaxElems < max_elems ? kOneShotMaxElems : max_elems) / kGroup + 1;
+    L.slot_groups = shard > one ? shard : one;
+    L.off_q = 0;
+    L.off_s = round_up(L.off_q + 2 * static_cast<size_t>(world) * L.slot_groups * kGroup, 256);
+    L.off_gather = round_up(L.off_s + 2 * static_cast<size_t>(world) * L.slot_groups * 4 * sizeof(float), 256);
+    L.off_flags = round_up(L.off_gather + groups * kGroup * 2, 256);
+    L.bytes = L.off_flags + 1024;
+    return L;
+}
+
+struct Ctx {
+    int rank, world;
+    size_t max_elems;
+    Layout L;
+    uint8_t* ws[kMaxWorld];
+    unsigned epoch;
+};
+
+struct KParams {
+    uint8_t* ws[kMaxWorld];
+    Layout L;
+    int rank, world;
+    size_t n;            // elements (multiple of 128)
+    size_t groups;       // ceil(n / 512)
+    unsigned epoch;
+    int one_shot;
+    const __nv_bfloat16* x;
+    __nv_bfloat16* out;  // may be nullptr (two-shot: result stays in the gather area)
+    int* status;
+};
+
+__device__ __forceinline__ size_t group_begin(int r, size_t groups, int world) { return groups * r / world; }
+
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+    unsigned v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Encodes 16 consecutive elements held by this lane; the 8 lanes that share a
+// 128-element block agree on its scale.  Returns the 16 encoded bytes.
+__device__ __forceinline__ uint4 encode16(const uint4 lo, const uint4 hi, bool valid, float& scale_out) {
+    float v[16];
+    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        v[2 * i] = valid ? __uint_as_float(w[i] << 16) : 0.0f;
+        v[2 * i + 1] = valid ? __uint_as_float(w[i] & 0xFFFF0000u) : 0.0f;
+    }
+    float amax = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; i++) amax = fmaxf(amax, fabsf(v[i]));
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float s = amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+    scale_out = s;
+    uint32_t q[4];
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const __nv_fp8x2_storage_t a =
+            __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[4 * i], s), __fdiv_rn(v[4 * i + 1], s)), __NV_SATFINITE, __NV_E4M3);
+        const __nv_fp8x2_storage_t b =
+            __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[4 * i + 2], s), __fdiv_rn(v[4 * i + 3], s)), __NV_SATFINITE, __NV_E4M3);
+        q[i] = static_cast<uint32_t>(a) | (static_cast<uint32_t>(b) << 16);
+    }
+    return make_uint4(q[0], q[1], q[2], q[3]);
+}
+
+__device__ __forceinline__ void decode16(const uint4 q, float* v) {
+    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const __half2_raw r = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>((w[i] >> (16 * h)) & 0xFFFFu), __NV_E4M3);
+            const __half2 hh = *reinterpret_cast<const __half2*>(&r);
+            const float2 f = __half22float2(hh);
+            v[4 * i + 2 * h] = f.x;
+            v[4 * i + 2 * h + 1] = f.y;
+        }
+    }
+}
+
+// Called by every block at the end of a producing phase: the last block of the
+// grid to get here (counted in a word of the own workspace, after a system-wide
+// fence) publishes `epoch` in word [which][my rank] of every rank's flag block.
+// Publishing at the end of the producer - not at the start of the consumer -
+// means a consumer launch never depends on a launch issued after it.
+__device__ __forceinline__ void publish_when_grid_done(const KParams& p, int which) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        unsigned* cnt = reinterpret_cast<unsigned*>(p.ws[p.rank] + p.L.off_flags) + 64 + which;
+        const unsigned old = atomicAdd(cnt, 1u);
+        if (old == gridDim.x - 1) {
+            *cnt = 0;                          // ready for the next launch
+            __threadfence_system();
+            for (int peer = 0; peer < p.world; peer++) {
+                unsigned* f = reinterpret_cast<unsigned*>(p.ws[peer] + p.L.off_flags) + which * kMaxWorld + p.rank;
+                st_release_sys(f, p.epoch);
+            }
+        }
+    }
+}
+
+// Every block waits (bounded) until all ranks have published `epoch` in row
+// `which` of this rank's flag block.  Returns false on timeout.
+__device__ __forceinline__ bool wait_flags(const KParams& p, int which) {
+    __shared__ int ok_s;
+    if (threadIdx.x == 0) {
+        const unsigned* mine = reinterpret_cast<const unsigned*>(p.ws[p.rank] + p.L.off_flags) + which * kMaxWorld;
+        bool ok = true;
+        const uint64_t t0 = globaltimer_ns();
+        for (int r = 0; r < p.world && ok; r++) {
+            unsigned spins = 0;
+            // epochs only grow; a flag at or beyond this call's epoch means "arrived"
+            while (static_cast<int>(ld_acquire_sys(mine + r) - p.epoch) < 0) {
+                if ((++spins & 0xFF) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) { ok = false; break; }
+            }
+        }
+        if (!ok) report_timeout(p.status);
+        ok_s = ok ? 1 : 0;
+    }
+    __syncthreads();
+    return ok_s != 0;
+}
+
+// ------------------------------------------------------------------ phase 1
+// One warp per 512-element group: lane l holds elements [16 l, 16 l + 16).
+__global__ void __launch_bounds__(kThreads) ar_push_kernel(const KParams p) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
+    const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
+    for (size_t g = warp; g < p.groups; g += nwarps) {
+        const size_t e0 = g * kGroup + static_cast<size_t>(lane) * 16;
+        const bool valid = e0 < p.n;            // n is a multiple of 128, so validity is per 128-block
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+        if (valid) {
+            const uint4* src = reinterpret_cast<const uint4*>(p.x + e0);
+            lo = __ldg(src);
+            hi = __ldg(src + 1);
+        }
+        float s;
+        const uint4 q = encode16(lo, hi, valid, s);
+        // the four block scales of the group, gathered on lane 0
+        const float s1 = __shfl_sync(0xffffffffu, s, 8), s2 = __shfl_sync(0xffffffffu, s, 16),
+                    s3 = __shfl_sync(0xffffffffu, s, 24);
+        int first, last;
+        size_t slot_g;
+        if (p.one_shot) { first = 0; last = p.world - 1; slot_g = g; }
+        else {
+            int o = static_cast<int>((g * p.world + p.world - 1) / p.groups);   // owner: largest o with begin(o) <= g
+            while (o + 1 < p.world && group_begin(o + 1, p.groups, p.world) <= g) o++;
+            while (o > 0 && group_begin(o, p.groups, p.world) > g) o--;
+            first = last = o;
+            slot_g = g - group_begin(o, p.groups, p.world);
+        }
+        const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + p.rank) * p.L.slot_groups + slot_g;
+        for (int peer = first; peer <= last; peer++) {
+            uint8_t* base = p.ws[peer];
+            uint4* dq = reinterpret_cast<uint4*>(base + p.L.off_q + slot * kGroup) + lane;
+            *dq = q;
+            if (lane == 0) {
+                float4* ds = reinterpret_cast<float4*>(base + p.L.off_s) + slot;
+                *ds = make_float4(s, s1, s2, s3);
+            }
+        }
+    }
+    publish_when_grid_done(p, 0);
+}
+
+// ------------------------------------------------------------------ phase 2
+__global__ void __launch_bounds__(kThreads) ar_reduce_kernel(const KParams p) {
+    const bool arrived = wait_flags(p, 0);
+    const int lane = threadIdx.x & 31;
+    const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
+    const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
+    const size_t gb = p.one_shot ? 0 : group_begin(p.rank, p.groups, p.world);
+    const size_t ge = p.one_shot ? p.groups : group_begin(p.rank + 1, p.groups, p.world);
+    const uint8_t* mine = p.ws[p.rank];
+    for (size_t g = gb + warp; arrived && g < ge; g += nwarps) {
+        const size_t slot_g = g - gb;
+        float acc[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) acc[i] = 0.0f;
+        for (int r = 0; r < p.world; r++) {
+            const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + r) * p.L.slot_groups + slot_g;
+            const uint4 q = __ldcg(reinterpret_cast<const uint4*>(mine + p.L.off_q + slot * kGroup) + lane);
+            const float s = __ldcg(reinterpret_cast<const float*>(mine + p.L.off_s) + slot * 4 + (lane >> 3));
+            float v[16];
+            decode16(q, v);
+#pragma unroll
+            for (int i = 0; i < 16; i++) acc[i] = __fadd_rn(acc[i], __fmul_rn(v[i], s));   // product and sum rounded separately
+        }
+        uint32_t o[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+            o[i] = *reinterpret_cast<const uint32_t*>(&b);
+        }
+        const size_t e0 = g * kGroup + static_cast<size_t>(lane) * 16;
+        if (e0 >= p.n) continue;
+        const uint4 lo = make_uint4(o[0], o[1], o[2], o[3]), hi = make_uint4(o[4], o[5], o[6], o[7]);
+        if (p.one_shot) {
+            uint4* d = reinterpret_cast<uint4*>(p.out + e0);
+            d[0] = lo;
+            d[1] = hi;
+        } else {
+            for (int peer = 0; peer < p.world; peer++) {
+                uint4* d = reinterpret_cast<uint4*>(p.ws[peer] + p.L.off_gather + e0 * 2);
+                d[0] = lo;
+                d[1] = hi;
+            }
+        }
+    }
+    if (!p.one_shot) publish_when_grid_done(p, 1);   // also after a timeout, so that peers are not left waiting
+}
+
+// ------------------------------------------------------------------ phase 3
+__global__ void __launch_bounds__(kThreads) ar_gather_kernel(const KParams p) {
+    if (!wait_flags(p, 1)) return;
+    if (p.out == nullptr) return;
+    const uint4* src = reinterpret_cast<const uint4*>(p.ws[p.rank] + p.L.off_gather);
+    uint4* dst = reinterpret_cast<uint4*>(p.out);
+    const size_t n16 = p.n / 8;
+    for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x)
+        dst[i] = __ldcg(src + i);
+}
+
+// Standalone encoder (the quantise step alone, for bit-exact tests and callers
+// that want the encoding): q [n] bytes, scales [n/128].
+__global__ void __launch_bounds__(kThreads) quantize_blocks128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
+                                                                     float* __restrict__ scales, size_t n, size_t groups) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
+    const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
+    for (size_t g = warp; g < groups; g += nwarps) {
+        const size_t e0 = g * kGroup + static_cast<size_t>(lane) * 16;
+        const bool valid = e0 < n;
+        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+        if (valid) {
+            lo = __ldg(reinterpret_cast<const uint4*>(x + e0));
+            hi = __ldg(reinterpret_cast<const uint4*>(x + e0) + 1);
+        }
+        float s;
+        const uint4 enc = encode16(lo, hi, valid, s);
+        if (valid) {
+            *reinterpret_cast<uint4*>(q + e0) = enc;
+            if ((lane & 7) == 0) scales[e0 / 128] = s;
+        }
+    }
+}
+
+static int grid_for(size_t warps_needed, int sm_count) {
+    size_t blocks = (warps_needed * 32 + kThreads - 1) / kThreads;
+    const size_t cap = static_cast<size_t>(sm_count) * 4;
+    if (blocks > cap) blocks = cap;
+    if (blocks < 1) blocks = 1;
+    return static_cast<int>(blocks);
+}
+
+static int run_phase(Ctx* c, int phase, const uint16_t* x, uint16_t* out, size_t n, int algo, unsigned epoch,
+                     cudaStream_t stream) {
+    int err = 0;
+    DeviceInfo* info = device_info(&err);
+    if (!info) return err;
+    KParams p;
+    memcpy(p.ws, c->ws, sizeof(p.ws));
+    p.L = c->L;
+    p.rank = c->rank;
+    p.world = c->world;
+    p.n = n;
+    p.groups = (n + kGroup - 1) / kGroup;
+    p.epoch = epoch;
+    p.one_shot = algo == 1 ? 1 : 0;
+    p.x = reinterpret_cast<const __nv_bfloat16*>(x);
+    p.out = reinterpret_cast<__nv_bfloat16*>(out);
+    p.status = info->status_dev;
+    if (phase == 1) {
+        ar_push_kernel<<<grid_for(p.groups, info->sm_count), kThreads, 0, stream>>>(p);
+    } else if (phase == 2) {
+        const size_t mine = p.one_shot ? p.groups : (p.groups + c->world - 1) / c->world;
+        ar_reduce_kernel<<<grid_for(mine, info->sm_count), kThreads, 0, stream>>>(p);
+    } else {
+        if (p.one_shot) return RDB_SUCCESS;          // the one-shot result is already in `out`
+        ar_gather_kernel<<<grid_for(p.out ? n / 8 / 32 + 1 : 1, info->sm_count), kThreads, 0, stream>>>(p);
+    }
+    return cudaGetLastError() == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
+}
+
+static int check_call(Ctx* c, const uint16_t* x, uint16_t* out, size_t n, int& algo) {
+    if (!c) return RDB_INVALID_CONFIG;
+    if (n == 0 || n % 128 != 0) return RDB_BAD_SHAPE;
+    if (n > c->max_elems) return RDB_SIZE_ABOVE_LIMIT;
+    if (!aligned16(x) || (out && !aligned16(out))) return RDB_BAD_ALIGNMENT;
+    if (algo == 0) algo = (n <= kOneShotMaxElems / 4) ? 1 : 2;
+    if (algo == 1 && n > kOneShotMaxElems) return RDB_SIZE_ABOVE_LIMIT;
+    if (algo == 1 && out == nullptr) return RDB_INVALID_CONFIG;
+    if (algo != 1 && algo != 2) return RDB_INVALID_CONFIG;
+    return RDB_SUCCESS;
+}
+
+}  // namespace ar
+}  // namespace rdb
+
+extern "C" {
+
+size_t rdb_ar_workspace_bytes(int world, size_t max_elems) {
+    if (world < 1 || world > rdb::ar::kMaxWorld || max_elems == 0) return 0;
+    return rdb::ar::make_layout(world, max_elems).bytes;
+}
+
+int rdb_ar_workspace_alloc(size_t bytes, void** ptr) {
+    if (!ptr || bytes == 0) return RDB_BAD_SHAPE;
+    if (cudaMalloc(ptr, bytes) != cudaSuccess) return RDB_CUDA_ERROR;
+    if (cudaMemset(*ptr, 0, bytes) != cudaSuccess) return RDB_CUDA_ERROR;
+    return cudaDeviceSynchronize() == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
+}
+
+int rdb_ar_workspace_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR; }
+
+int rdb_ar_ipc_export(void* ptr, uint8_t* handle64) {
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) return RDB_CUDA_ERROR;
+    memcpy(handle64, &h, sizeof(h));
+    return RDB_SUCCESS;
+}
+
+int rdb_ar_ipc_import(const uint8_t* handle64, void** ptr) {
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof(h));
+    return cudaIpcOpenMemHandle(ptr, h, cudaIpcMemLazyEnablePeerAccess) == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
+}
+
+int rdb_ar_ipc_close(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR; }
+
+int rdb_ar_create(int rank, int world, void* const* workspaces, size_t max_elems, void** ctx) {
+    if (!ctx || !workspaces || world < 1 || world > rdb::ar::kMaxWorld || rank < 0 || rank >= world || max_elems == 0)
+        return RDB_INVALID_CONFIG;
+    rdb::ar::Ctx* c = new rdb::ar::Ctx();
+    c->rank = rank;
+    c->world = world;
+    c->max_elems = max_elems;
+    c->L = rdb::ar::make_layout(world, max_elems);
+    for (int i = 0; i < rdb::ar::kMaxWorld; i++) c->ws[i] = i < world ? static_cast<uint8_t*>(workspaces[i]) : nullptr;
+    c->epoch = 0;
+    *ctx = c;
+    return RDB_SUCCESS;
+}
+
+int rdb_ar_destroy(void* ctx) {
+    delete static_cast<rdb::ar::Ctx*>(ctx);
+    return RDB_SUCCESS;
+}
+
+int rdb_ar_allreduce(void* ctx, const uint16_t* x, uint16_t* out, size_t n, int algo, void* stream) {
+    rdb::ar::Ctx* c = static_cast<rdb::ar::Ctx*>(ctx);
+    int r = rdb::ar::check_call(c, x, out, n, algo);
+    if (r != RDB_SUCCESS) return r;
+    const unsigned epoch = ++c->epoch;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    for (int phase = 1; phase <= 3; phase++) {
+        r = rdb::ar::run_phase(c, phase, x, out, n, algo, epoch, s);
+        if (r != RDB_SUCCESS) return r;
+    }
+    return RDB_SUCCESS;
+}
+
+int rdb_ar_begin_call(void* ctx) {
+    rdb::ar::Ctx* c = static_cast<rdb::ar::Ctx*>(ctx);
+    if (!c) return -1;
+    return static_cast<int>(++c->epoch);
+}
+
+int rdb_ar_phase(void* ctx, int phase, int epoch, const uint16_t* x, uint16_t* out, size_t n, int algo, void* stream) {
+    rdb::ar::Ctx* c = static_cast<rdb::ar::Ctx*>(ctx);
+    int r = rdb::ar::check_call(c, x, out, n, algo);
+    if (r != RDB_SUCCESS) return r;
+    if (phase < 1 || phase > 3 || epoch < 1) return RDB_INVALID_CONFIG;
+    return rdb::ar::run_phase(c, phase, x, out, n, algo, static_cast<unsigned>(epoch), static_cast<cudaStream_t>(stream));
+}
+
+const uint16_t* rdb_ar_result(void* ctx) {
+    rdb::ar::Ctx* c = static_cast<rdb::ar::Ctx*>(ctx);
+    if (!c) return nullptr;
+    return reinterpret_cast<const uint16_t*>(c->ws[c->rank] + c->L.off_gather);
+}
+
+int rdb_quantize_blocks128(const uint16_t* x, uint8_t* q, float* scales, size_t n, void* stream) {
+    if (n == 0 || n % 128 != 0) return RDB_BAD_SHAPE;
+    if (!rdb::aligned16(x) || !rdb::aligned16(q)) return RDB_BAD_ALIGNMENT;
+    int err = 0;
+    rdb::DeviceInfo* info = rdb::device_info(&err);
+    if (!info) return err;
+    const size_t groups = (n + rdb::ar::kGroup - 1) / rdb::ar::kGroup;
+    rdb::ar::quantize_blocks128_kernel<<<rdb::ar::grid_for(groups, info->sm_count), rdb::ar::kThreads, 0,
+                                         static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const __nv_bfloat16*>(x), q, scales, n, groups);
+    return cudaGetLastError() == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
+}
+
+}  // extern "C"

@@ -1,0 +1,42 @@
+"""One rank of the multi-GPU allreduce test (launched by test_allreduce.py):
+runs the FP8-encoded allreduce for several sizes and both algorithms and
+compares every result, bit for bit, with the CPU oracle."""
+import os
+import sys
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo")          # handles travel over gloo; the data path is the library's own
+    import rocm_dev_b200 as R
+    from oracle import oracle as O
+    ar = R.Fp8AllReduce(max_elems=4096 * 8192)
+    dev = torch.device("cuda", rank)
+    cases = [(128, 1), (8192, 1), (8192, 2), (16 * 8192, 0), (128 * 8192, 2), (640, 2), (1024 * 8192, 0)]
+    for n, algo in cases:
+        for rep in range(2):                 # twice: both staging sets, growing epochs
+            xs = [torch.randn(n, generator=torch.Generator().manual_seed(1000 * rep + 17 * r + n)).bfloat16()
+                  for r in range(world)]
+            out = ar.all_reduce(xs[rank].to(dev), algo=algo)
+            torch.cuda.synchronize()
+            assert R.lib().rdb_device_status() == 0, "device-side wait timed out"
+            bits = np.stack([x.view(torch.int16).numpy().view(np.uint16) for x in xs])
+            want, _, _ = O.allreduce_fp8(bits)
+            got = out.cpu().view(torch.int16).numpy().view(np.uint16)
+            assert np.array_equal(got, want), f"rank {rank} n {n} algo {algo} rep {rep}: {(got != want).sum()} differ"
+    dist.barrier()
+    ar.close()
+    dist.destroy_process_group()
+    print(f"rank {rank} ok")
+
+
+if __name__ == "__main__":
+    main()

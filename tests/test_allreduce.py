@@ -1,0 +1,165 @@
+"""FP8-encoded allreduce.  The encoding must be bit-exact; because the kernels
+round the product and the rank-ordered sum separately, as the oracle does, the
+reduced bf16 result is compared bit for bit as well (stricter than the stated
+tolerance of 1e-2 relative Frobenius / 2 bf16 ulp)."""
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _bits(t):
+    return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
+
+
+# ------------------------------------------------------------- CPU (gloo)
+def _gloo_rank(rank, world, port, n, q):
+    """The protocol of the two-shot algorithm acted out by CPU ranks with the
+    oracle's arithmetic: encode, scatter shards, reduce in rank order, gather."""
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    from oracle import oracle as O
+    from rocm_dev_b200.allreduce import GROUP, shard_groups
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    x = torch.randn(n, generator=torch.Generator().manual_seed(rank)).bfloat16()
+    enc_q, enc_s = O.quantize_blocks128(_bits(x))
+    qs = [torch.empty(n, dtype=torch.uint8) for _ in range(world)]
+    ss = [torch.empty(n // 128) for _ in range(world)]
+    dist.all_gather(qs, torch.from_numpy(enc_q))
+    dist.all_gather(ss, torch.from_numpy(enc_s))
+    gb, ge = shard_groups(n, world)[rank]
+    lo, hi = gb * GROUP, min(ge * GROUP, n)
+    acc = np.zeros(hi - lo, np.float32)
+    for r in range(world):                    # rank order; product and sum rounded separately
+        deq = (O.e4m3fn_decode(qs[r].numpy()[lo:hi]) * np.repeat(ss[r].numpy()[lo // 128:hi // 128], 128)).astype(np.float32)
+        acc = (acc + deq).astype(np.float32)
+    mine = torch.from_numpy(O.bf16_encode(acc).astype(np.int32))
+    sizes = [min(e * GROUP, n) - b * GROUP for b, e in shard_groups(n, world)]
+    parts = [torch.empty(s, dtype=torch.int32) for s in sizes]
+    dist.all_gather(parts, mine) if len(set(sizes)) == 1 else dist.all_gather_object(parts, mine)
+    q.put((rank, torch.cat([p if isinstance(p, torch.Tensor) else p for p in parts]).numpy().astype(np.uint16)))
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("n", [1024, 128 * 37])
+def test_two_rank_protocol_on_cpu(oracle, n):
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + (os.getpid() + n) % 1000
+    procs = [ctx.Process(target=_gloo_rank, args=(r, 2, port, n, q)) for r in range(2)]
+    [p.start() for p in procs]
+    res = dict(q.get(timeout=120) for _ in range(2))
+    [p.join(timeout=60) for p in procs]
+    xs = np.stack([_bits(torch.randn(n, generator=torch.Generator().manual_seed(r)).bfloat16()) for r in range(2)])
+    want, _, _ = oracle.allreduce_fp8(xs)
+    assert np.array_equal(res[0], want) and np.array_equal(res[1], want)
+
+
+def test_shard_groups_cover_every_group_once():
+    from rocm_dev_b200.allreduce import shard_groups
+    for n in (128, 512, 640, 8192, 8192 * 4096, 128 * 999):
+        for w in range(1, 9):
+            sh = shard_groups(n, w)
+            assert sh[0][0] == 0 and sh[-1][1] == (n + 511) // 512
+            assert all(a[1] == b[0] for a, b in zip(sh, sh[1:]))
+            assert max(e - b for b, e in sh) - min(e - b for b, e in sh) <= 1
+
+
+# ------------------------------------------------------------------ GPU
+@pytest.mark.gpu
+@pytest.mark.parametrize("n", [128, 512, 640, 8192, 128 * 1001])
+def test_encoder_is_bit_exact(cuda_device, oracle, n):
+    import rocm_dev_b200 as R
+    x = torch.randn(n, generator=torch.Generator().manual_seed(n)).bfloat16()
+    x[:128] = 0                                            # an all-zero block: scale 1
+    if n > 300:
+        x[200] = 3.0e38
+        x[300] = -1.0e-30
+    q, s = R.quantize_blocks128(x.to(cuda_device))
+    wq, ws = oracle.quantize_blocks128(_bits(x))
+    assert np.array_equal(q.cpu().numpy(), wq)
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
+@pytest.mark.parametrize("algo", [1, 2])
+def test_emulated_ranks_on_one_gpu(cuda_device, oracle, world, algo):
+    import rocm_dev_b200 as R
+    lr = R.LocalRanks(world, max_elems=1 << 20, device=cuda_device)
+    try:
+        for n in (128, 640, 8192, 128 * 517, 1 << 20):
+            for rep in range(2):
+                xs = [torch.randn(n, generator=torch.Generator().manual_seed(100 * rep + r)).bfloat16() for r in range(world)]
+                outs = lr.all_reduce([x.to(cuda_device) for x in xs], algo=algo)
+                torch.cuda.synchronize()
+                assert R.lib().rdb_device_status() == 0
+                want, _, _ = oracle.allreduce_fp8(np.stack([_bits(x) for x in xs]))
+                for r in range(world):
+                    assert np.array_equal(_bits(outs[r]), want), (world, algo, n, rep, r)
+    finally:
+        lr.close()
+
+
+@pytest.mark.gpu
+def test_full_size_properties(cuda_device, oracle):
+    """64 MB per rank (T = 4096 rows of 8192): close to the exact sum, identical
+    on all ranks, and scaling the inputs by a power of two scales the result."""
+    import rocm_dev_b200 as R
+    world, n = 4, 4096 * 8192
+    lr = R.LocalRanks(world, max_elems=n, device=cuda_device)
+    try:
+        xs = [torch.randn(n, generator=torch.Generator(device=cuda_device).manual_seed(r), device=cuda_device).bfloat16()
+              for r in range(world)]
+        outs = lr.all_reduce(xs, algo=2)
+        exact = sum(x.float() for x in xs)
+        rel = (outs[0].float() - exact).norm() / exact.norm()
+        assert rel < 5e-2                                   # two e4m3 roundings per term, not an exact sum
+        assert all(torch.equal(outs[0], o) for o in outs[1:])
+        outs4 = lr.all_reduce([4 * x for x in xs], algo=2)
+        assert torch.equal(outs4[0].float(), 4 * outs[0].float())
+        rows = slice(0, 8192 * 3)                           # the oracle on the first rows
+        want, _, _ = oracle.allreduce_fp8(np.stack([_bits(x[rows]) for x in xs]))
+        assert np.array_equal(_bits(outs[0][rows]), want)
+    finally:
+        lr.close()
+
+
+@pytest.mark.gpu
+def test_error_codes(cuda_device):
+    import ctypes as C
+    import rocm_dev_b200 as R
+    L = R.lib()
+    lr = R.LocalRanks(2, max_elems=4096, device=cuda_device)
+    try:
+        x = torch.zeros(8192, dtype=torch.bfloat16, device=cuda_device)
+        assert L.rdb_ar_allreduce(lr.ctx[0], x.data_ptr(), x.data_ptr(), 100, 0, 0) == 8       # not a multiple of 128
+        assert L.rdb_ar_allreduce(lr.ctx[0], x.data_ptr(), x.data_ptr(), 8192, 0, 0) == 11     # above max_elems
+        assert L.rdb_ar_allreduce(lr.ctx[0], x.data_ptr() + 2, x.data_ptr(), 128, 0, 0) == 7
+        assert L.rdb_ar_allreduce(lr.ctx[0], x.data_ptr(), None, 128, 1, 0) == 6               # one-shot needs out
+        assert L.rdb_ar_workspace_bytes(9, 128) == 0
+        ctx = C.c_void_p()
+        assert L.rdb_ar_create(2, 2, (C.c_void_p * 2)(), 128, C.byref(ctx)) == 6
+    finally:
+        lr.close()
+
+
+@pytest.mark.gpu
+def test_two_processes_two_gpus(cuda_device):
+    """Real peer-to-peer path: one process per GPU, workspaces shared by IPC."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(29600 + os.getpid() % 300), WORLD_SIZE="2",
+               NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "ar_worker.py")], env=dict(env, RANK=str(r)),
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)
+    assert all(f"rank {r} ok" in outs[r] for r in range(2))
