@@ -172,6 +172,7 @@ def run_gpu(args):
     dev = torch.device("cuda", local)
     R.lib()
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # keep stdout for the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     # synthetic operands with the value distribution of quantised N(0,1) / N(0,0.02)
@@ -321,6 +322,10 @@ def run_gpu(args):
                "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": n_e2e,
                "note": "weights, activations and scales copied from pinned host memory for every call"}
 
+    allreduce = None
+    if world > 1 and not args.no_allreduce:
+        allreduce = bench_allreduce(torch, dist, R, dev, rank, world)
+
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
@@ -354,9 +359,51 @@ def run_gpu(args):
         "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": launches_per_step * args.steps, "clocks": clocks,
         "detail": detail,
     }
+    if allreduce is not None:
+        line["allreduce"] = allreduce
     print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
+
+
+def bench_allreduce(torch, dist, R, dev, rank, world):
+    """FP8-encoded allreduce against NCCL's bf16 allreduce on [T, 8192] bf16
+    tensors.  busBW = S/t * 2(n-1)/n with S the bf16 size; device time, max over
+    ranks.  Reported beside the headline metric when more than one GPU runs."""
+    ar = R.Fp8AllReduce(max_elems=4096 * 8192)
+    out = {"unit": "GB/s busBW", "world": world, "cases": {}}
+
+    def timed(fn, iters):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        dist.barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([a.elapsed_time(b) / iters], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item()) * 1e-3
+
+    for T in (1, 16, 128, 1024, 4096):
+        n = T * 8192
+        x = torch.randn(n, generator=torch.Generator(device=dev).manual_seed(rank), device=dev).bfloat16()
+        y = torch.empty_like(x)
+        z = x.clone()
+        iters = 200 if T <= 128 else 40
+        t_fp8 = timed(lambda: ar.all_reduce(x, out=y), iters)
+        t_nccl = timed(lambda: dist.all_reduce(z), iters)
+        S, f = n * 2, 2 * (world - 1) / world
+        out["cases"][f"T{T}"] = {"bytes": S, "fp8_us": round(t_fp8 * 1e6, 2), "nccl_bf16_us": round(t_nccl * 1e6, 2),
+                                 "fp8_busbw": round(S / t_fp8 * f / 1e9, 1), "nccl_bf16_busbw": round(S / t_nccl * f / 1e9, 1),
+                                 "ratio": round(t_nccl / t_fp8, 3)}
+    if R.lib().rdb_device_status() != 0:
+        out["error"] = "device status word reports a timed-out wait"
+    ar.close()
+    return out
 
 
 def main():
@@ -369,6 +416,7 @@ def main():
     ap.add_argument("--no-detail", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-allreduce", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
