@@ -39,37 +39,37 @@
 
 /* ------------------------------------------------- minimal parallel-for */
 /* Rows of independent work are spread over POSIX threads (the image has no
- * OpenMP runtime).  RDB_ORACLE_THREADS overrides the online-core count. */
-typedef void (*rdb_range_fn)(size_t lo, size_t hi, void *ctx);
-typedef struct { rdb_range_fn fn; void *ctx; size_t lo, hi; } rdb_job;
+ * OpenMP runtime).  ORC_ORACLE_THREADS overrides the online-core count. */
+typedef void (*orc_range_fn)(size_t lo, size_t hi, void *ctx);
+typedef struct { orc_range_fn fn; void *ctx; size_t lo, hi; } orc_job;
 
-int rdb_num_threads(void)
+int orc_num_threads(void)
 {
-    const char *e = getenv("RDB_ORACLE_THREADS");
+    const char *e = getenv("ORC_ORACLE_THREADS");
     long n = e ? atol(e) : sysconf(_SC_NPROCESSORS_ONLN);
     if (n < 1) n = 1;
     if (n > 256) n = 256;
     return (int)n;
 }
 
-static void *rdb_job_main(void *p) { rdb_job *j = (rdb_job *)p; j->fn(j->lo, j->hi, j->ctx); return NULL; }
+static void *orc_job_main(void *p) { orc_job *j = (orc_job *)p; j->fn(j->lo, j->hi, j->ctx); return NULL; }
 
-static void rdb_parallel_for(size_t n, rdb_range_fn fn, void *ctx)
+static void orc_parallel_for(size_t n, orc_range_fn fn, void *ctx)
 {
-    int nt = rdb_num_threads();
+    int nt = orc_num_threads();
     if ((size_t)nt > n) nt = n ? (int)n : 1;
     if (nt <= 1) { fn(0, n, ctx); return; }
     pthread_t th[256];
-    rdb_job jobs[256];
+    orc_job jobs[256];
     for (int t = 0; t < nt; t++) {
         jobs[t].fn = fn; jobs[t].ctx = ctx;
         jobs[t].lo = n * (size_t)t / nt; jobs[t].hi = n * (size_t)(t + 1) / nt;
-        if (pthread_create(&th[t], NULL, rdb_job_main, &jobs[t]) != 0) { fn(jobs[t].lo, jobs[t].hi, ctx); th[t] = 0; }
+        if (pthread_create(&th[t], NULL, orc_job_main, &jobs[t]) != 0) { fn(jobs[t].lo, jobs[t].hi, ctx); th[t] = 0; }
     }
     for (int t = 0; t < nt; t++) if (th[t]) pthread_join(th[t], NULL);
 }
 
-#define RDB_E4M3_MAX 448.0f
+#define ORC_E4M3_MAX 448.0f
 
 /* ------------------------------------------------------------------ codecs */
 
@@ -78,7 +78,7 @@ static uint32_t f32_bits(float f) { uint32_t u; memcpy(&u, &f, 4); return u; }
 
 /* e4m3fn: 1 sign, 4 exponent (bias 7), 3 mantissa; no infinities;
  * S.1111.111 is NaN; largest finite S.1111.110 = 448; subnormal step 2^-9. */
-float rdb_e4m3fn_decode(uint8_t b)
+float orc_e4m3fn_decode(uint8_t b)
 {
     const int sign = b >> 7, e = (b >> 3) & 0xF, m = b & 7;
     float v;
@@ -90,13 +90,13 @@ float rdb_e4m3fn_decode(uint8_t b)
 
 /* Saturating round-to-nearest-even conversion (the __HIP_SATFINITE rule of
  * projects/common.cuh:103 applied to the e4m3fn grid).  NaN -> 0x7F. */
-uint8_t rdb_e4m3fn_encode(float x)
+uint8_t orc_e4m3fn_encode(float x)
 {
     const uint32_t u = f32_bits(x);
     const uint8_t sign = (uint8_t)((u >> 24) & 0x80);
     const float a = fabsf(x);
     if (x != x) return 0x7F;
-    if (a >= RDB_E4M3_MAX) return sign | 0x7E;          /* saturate (also +-inf) */
+    if (a >= ORC_E4M3_MAX) return sign | 0x7E;          /* saturate (also +-inf) */
     if (a < ldexpf(1.0f, -6)) {
         /* subnormal range: grid step 2^-9; rintf honours round-half-even */
         const float q = rintf(a * 512.0f);               /* exact scaling */
@@ -115,7 +115,7 @@ uint8_t rdb_e4m3fn_encode(float x)
 }
 
 /* bf16 = upper 16 bits of fp32, round-to-nearest-even; NaN stays NaN. */
-uint16_t rdb_bf16_encode(float x)
+uint16_t orc_bf16_encode(float x)
 {
     uint32_t u = f32_bits(x);
     if (x != x) return (uint16_t)((u >> 16) | 0x0040);
@@ -123,53 +123,53 @@ uint16_t rdb_bf16_encode(float x)
     return (uint16_t)(u >> 16);
 }
 
-float rdb_bf16_decode(uint16_t h) { return f32_from_bits((uint32_t)h << 16); }
+float orc_bf16_decode(uint16_t h) { return f32_from_bits((uint32_t)h << 16); }
 
-void rdb_e4m3fn_decode_n(const uint8_t *q, float *out, size_t n)
+void orc_e4m3fn_decode_n(const uint8_t *q, float *out, size_t n)
 {
-    for (size_t i = 0; i < n; i++) out[i] = rdb_e4m3fn_decode(q[i]);
+    for (size_t i = 0; i < n; i++) out[i] = orc_e4m3fn_decode(q[i]);
 }
 
-void rdb_e4m3fn_encode_n(const float *x, uint8_t *q, size_t n)
+void orc_e4m3fn_encode_n(const float *x, uint8_t *q, size_t n)
 {
-    for (size_t i = 0; i < n; i++) q[i] = rdb_e4m3fn_encode(x[i]);
+    for (size_t i = 0; i < n; i++) q[i] = orc_e4m3fn_encode(x[i]);
 }
 
-void rdb_bf16_encode_n(const float *x, uint16_t *out, size_t n)
+void orc_bf16_encode_n(const float *x, uint16_t *out, size_t n)
 {
-    for (size_t i = 0; i < n; i++) out[i] = rdb_bf16_encode(x[i]);
+    for (size_t i = 0; i < n; i++) out[i] = orc_bf16_encode(x[i]);
 }
 
 /* --------------------------------------------------------------- quantisers */
 
 /* Per-tensor: scale = amax/448 (1 when the tensor is all zero),
  * q = e4m3fn_sat_rn(x / scale) with an fp32 division. */
-void rdb_quantize_per_tensor(const float *x, size_t n, uint8_t *q, float *scale)
+void orc_quantize_per_tensor(const float *x, size_t n, uint8_t *q, float *scale)
 {
     float amax = 0.0f;
     for (size_t i = 0; i < n; i++) { const float a = fabsf(x[i]); if (a > amax) amax = a; }
-    const float s = amax > 0.0f ? amax / RDB_E4M3_MAX : 1.0f;
-    for (size_t i = 0; i < n; i++) q[i] = rdb_e4m3fn_encode(x[i] / s);
+    const float s = amax > 0.0f ? amax / ORC_E4M3_MAX : 1.0f;
+    for (size_t i = 0; i < n; i++) q[i] = orc_e4m3fn_encode(x[i] / s);
     *scale = s;
 }
 
 /* Per-128-element blocks over a bf16 vector; n must be a multiple of 128.
  * scales[b] = amax_b/448 (1 for an all-zero block). */
-void rdb_quantize_blocks128(const uint16_t *x_bf16, size_t n, uint8_t *q, float *scales)
+void orc_quantize_blocks128(const uint16_t *x_bf16, size_t n, uint8_t *q, float *scales)
 {
     for (size_t b = 0; b < n / 128; b++) {
         const uint16_t *xb = x_bf16 + b * 128;
         float amax = 0.0f;
-        for (int i = 0; i < 128; i++) { const float a = fabsf(rdb_bf16_decode(xb[i])); if (a > amax) amax = a; }
-        const float s = amax > 0.0f ? amax / RDB_E4M3_MAX : 1.0f;
-        for (int i = 0; i < 128; i++) q[b * 128 + i] = rdb_e4m3fn_encode(rdb_bf16_decode(xb[i]) / s);
+        for (int i = 0; i < 128; i++) { const float a = fabsf(orc_bf16_decode(xb[i])); if (a > amax) amax = a; }
+        const float s = amax > 0.0f ? amax / ORC_E4M3_MAX : 1.0f;
+        for (int i = 0; i < 128; i++) q[b * 128 + i] = orc_e4m3fn_encode(orc_bf16_decode(xb[i]) / s);
         scales[b] = s;
     }
 }
 
 /* -------------------------------------------------------------------- GEMMs */
 
-static void decode_table(float *t) { for (int i = 0; i < 256; i++) t[i] = rdb_e4m3fn_decode((uint8_t)i); }
+static void decode_table(float *t) { for (int i = 0; i < 256; i++) t[i] = orc_e4m3fn_decode((uint8_t)i); }
 
 /* D[i,j] = bf16( (sum_k a[i,k]*b[j,k], sequential fp32) * (scale_a*scale_b) ).
  * A is [M,K] row-major, B is [N,K] with row pitch ldb (K-contiguous).
@@ -193,14 +193,14 @@ static void gemm_rows(size_t lo, size_t hi, void *p)
             const float *a = c->Af + (size_t)i * K;
             float acc = 0.0f;
             for (int l = 0; l < K; l++) acc += a[l] * bf[l];       /* sequential, k order */
-            if (c->out_bf16) ((uint16_t *)c->D)[(size_t)i * c->N + j] = rdb_bf16_encode(acc * c->scale);
+            if (c->out_bf16) ((uint16_t *)c->D)[(size_t)i * c->N + j] = orc_bf16_encode(acc * c->scale);
             else ((float *)c->D)[(size_t)i * c->N + j] = acc;
         }
     }
     free(bf);
 }
 
-void rdb_gemm_fp8_bf16(const uint8_t *A, const uint8_t *B, float scale_a, float scale_b,
+void orc_gemm_fp8_bf16(const uint8_t *A, const uint8_t *B, float scale_a, float scale_b,
                        uint16_t *D, int M, int N, int K, int ldb)
 {
     float lut[256];
@@ -208,7 +208,7 @@ void rdb_gemm_fp8_bf16(const uint8_t *A, const uint8_t *B, float scale_a, float 
     float *Af = (float *)malloc((size_t)M * K * sizeof(float));
     for (size_t i = 0; i < (size_t)M * K; i++) Af[i] = lut[A[i]];
     gemm_ctx c = { B, Af, lut, D, NULL, A, scale_a * scale_b, M, N, K, ldb, 1 };
-    rdb_parallel_for((size_t)N, gemm_rows, &c);
+    orc_parallel_for((size_t)N, gemm_rows, &c);
     free(Af);
 }
 
@@ -236,25 +236,25 @@ static void gemm64_rows(size_t lo, size_t hi, void *p)
  * the adjudicator for per-element ulp checks.  Also returns sum_k |a*b|*scale
  * in `mag` (may be NULL), the magnitude the fp32 summation-order error of any
  * implementation is proportional to. */
-void rdb_gemm_fp8_f64(const uint8_t *A, const uint8_t *B, float scale_a, float scale_b,
+void orc_gemm_fp8_f64(const uint8_t *A, const uint8_t *B, float scale_a, float scale_b,
                       double *D, double *mag, int M, int N, int K, int ldb)
 {
     float lut[256];
     decode_table(lut);
     gemm_ctx c = { B, NULL, lut, D, mag, A, scale_a * scale_b, M, N, K, ldb, 0 };
-    rdb_parallel_for((size_t)N, gemm64_rows, &c);
+    orc_parallel_for((size_t)N, gemm64_rows, &c);
 }
 
 /* The async_gemm projects' oracle: fp32 result, no scale
  * (projects/async_gemm_16x16x64/test.cu:22-37). */
-void rdb_gemm_fp8_f32(const uint8_t *A, const uint8_t *B, float *D, int M, int N, int K)
+void orc_gemm_fp8_f32(const uint8_t *A, const uint8_t *B, float *D, int M, int N, int K)
 {
     float lut[256];
     decode_table(lut);
     float *Af = (float *)malloc((size_t)M * K * sizeof(float));
     for (size_t i = 0; i < (size_t)M * K; i++) Af[i] = lut[A[i]];
     gemm_ctx c = { B, Af, lut, D, NULL, A, 1.0f, M, N, K, K, 0 };
-    rdb_parallel_for((size_t)N, gemm_rows, &c);
+    orc_parallel_for((size_t)N, gemm_rows, &c);
     free(Af);
 }
 
@@ -262,7 +262,7 @@ void rdb_gemm_fp8_f32(const uint8_t *A, const uint8_t *B, float *D, int M, int N
 
 /* D[k] = sum_b (A[b,k] + B[b,k]) in batch order, fp32
  * (projects/tiled_sum_reduce/test.cu:13-25). */
-void rdb_tiled_sum_reduce(const float *A, const float *B, float *D, int b, int m, int n)
+void orc_tiled_sum_reduce(const float *A, const float *B, float *D, int b, int m, int n)
 {
     const size_t mn = (size_t)m * n;
     for (size_t k = 0; k < mn; k++) D[k] = 0.0f;
@@ -283,7 +283,7 @@ typedef struct {
 static void ar_encode_blocks(size_t lo, size_t hi, void *p)
 {
     const ar_ctx *c = (const ar_ctx *)p;     /* block index runs over [rank][block] */
-    rdb_quantize_blocks128(c->xs + lo * 128, (hi - lo) * 128, c->q + lo * 128, c->s + lo);
+    orc_quantize_blocks128(c->xs + lo * 128, (hi - lo) * 128, c->q + lo * 128, c->s + lo);
 }
 
 static void ar_reduce_blocks(size_t lo, size_t hi, void *p)
@@ -293,7 +293,7 @@ static void ar_reduce_blocks(size_t lo, size_t hi, void *p)
         float acc = 0.0f;
         for (int r = 0; r < c->nranks; r++)
             acc += c->lut[c->q[(size_t)r * c->n + i]] * c->s[(size_t)r * c->nb + i / 128];
-        c->out[i] = rdb_bf16_encode(acc);
+        c->out[i] = orc_bf16_encode(acc);
     }
 }
 
@@ -303,7 +303,7 @@ static void ar_reduce_blocks(size_t lo, size_t hi, void *p)
  * all ranks produce identical bits.  xs is nranks consecutive bf16 vectors of
  * n elements.  q_out / s_out (may be NULL) receive the encodings
  * [nranks][n] and [nranks][n/128] for bit-exact comparison. */
-void rdb_allreduce_fp8(const uint16_t *xs, int nranks, size_t n, uint16_t *out,
+void orc_allreduce_fp8(const uint16_t *xs, int nranks, size_t n, uint16_t *out,
                        uint8_t *q_out, float *s_out)
 {
     const size_t nb = n / 128;
@@ -312,8 +312,8 @@ void rdb_allreduce_fp8(const uint16_t *xs, int nranks, size_t n, uint16_t *out,
     float lut[256];
     decode_table(lut);
     ar_ctx c = { xs, q, s, lut, out, nranks, n, nb };
-    rdb_parallel_for((size_t)nranks * nb, ar_encode_blocks, &c);
-    rdb_parallel_for(nb, ar_reduce_blocks, &c);
+    orc_parallel_for((size_t)nranks * nb, ar_encode_blocks, &c);
+    orc_parallel_for(nb, ar_reduce_blocks, &c);
     if (!q_out) free(q);
     if (!s_out) free(s);
 }
@@ -322,7 +322,7 @@ void rdb_allreduce_fp8(const uint16_t *xs, int nranks, size_t n, uint16_t *out,
 
 /* Prune W [N,K] (fp32) in place: in each aligned group of 4 along K keep the 2
  * entries of largest magnitude (ties: lowest index) and zero the rest. */
-void rdb_prune_2of4(float *W, int N, int K)
+void orc_prune_2of4(float *W, int N, int K)
 {
     for (size_t g = 0; g < (size_t)N * K / 4; g++) {
         float *w = W + g * 4;
@@ -342,7 +342,7 @@ void rdb_prune_2of4(float *W, int N, int K)
  * group with fewer than two non-zero bytes keeps the lowest unused positions
  * so that the pair is always strictly ascending.  Returns the number of groups
  * that had more than two non-zero bytes (0 for a valid 2:4 matrix). */
-int rdb_compress_2of4(const uint8_t *Wq, int N, int K, uint8_t *vals, uint8_t *meta)
+int orc_compress_2of4(const uint8_t *Wq, int N, int K, uint8_t *vals, uint8_t *meta)
 {
     int bad = 0;
     for (size_t g = 0; g < (size_t)N * K / 4; g++) {
@@ -363,8 +363,8 @@ int rdb_compress_2of4(const uint8_t *Wq, int N, int K, uint8_t *vals, uint8_t *m
     return bad;
 }
 
-/* Inverse of rdb_compress_2of4. */
-void rdb_expand_2of4(const uint8_t *vals, const uint8_t *meta, int N, int K, uint8_t *Wq)
+/* Inverse of orc_compress_2of4. */
+void orc_expand_2of4(const uint8_t *vals, const uint8_t *meta, int N, int K, uint8_t *Wq)
 {
     for (size_t g = 0; g < (size_t)N * K / 4; g++) {
         uint8_t *w = Wq + g * 4;
@@ -377,7 +377,7 @@ void rdb_expand_2of4(const uint8_t *vals, const uint8_t *meta, int N, int K, uin
 /* ------------------------------------------------------------------ metrics */
 
 /* max and total absolute delta, as projects/skinny_gemm/test.cu:94-107. */
-void rdb_deltas(const float *x, const float *ref, size_t n, float *max_delta, float *total_delta)
+void orc_deltas(const float *x, const float *ref, size_t n, float *max_delta, float *total_delta)
 {
     float mx = 0.0f, sum = 0.0f;
     for (size_t i = 0; i < n; i++) {

@@ -33,14 +33,14 @@ def lib() -> C.CDLL:
     global _lib
     if _lib is None:
         _lib = C.CDLL(build())
-        _lib.rdb_e4m3fn_decode.restype = C.c_float
-        _lib.rdb_e4m3fn_decode.argtypes = [C.c_uint8]
-        _lib.rdb_e4m3fn_encode.restype = C.c_uint8
-        _lib.rdb_e4m3fn_encode.argtypes = [C.c_float]
-        _lib.rdb_bf16_encode.restype = C.c_uint16
-        _lib.rdb_bf16_encode.argtypes = [C.c_float]
-        _lib.rdb_compress_2of4.restype = C.c_int
-        _lib.rdb_num_threads.restype = C.c_int
+        _lib.orc_e4m3fn_decode.restype = C.c_float
+        _lib.orc_e4m3fn_decode.argtypes = [C.c_uint8]
+        _lib.orc_e4m3fn_encode.restype = C.c_uint8
+        _lib.orc_e4m3fn_encode.argtypes = [C.c_float]
+        _lib.orc_bf16_encode.restype = C.c_uint16
+        _lib.orc_bf16_encode.argtypes = [C.c_float]
+        _lib.orc_compress_2of4.restype = C.c_int
+        _lib.orc_num_threads.restype = C.c_int
     return _lib
 
 
@@ -53,21 +53,21 @@ def _c(a, dtype) -> np.ndarray:
 
 
 def num_threads() -> int:
-    return int(lib().rdb_num_threads())
+    return int(lib().orc_num_threads())
 
 
 # ------------------------------------------------------------------ codecs
 def e4m3fn_decode(q) -> np.ndarray:
     q = _c(q, np.uint8)
     out = np.empty(q.shape, np.float32)
-    lib().rdb_e4m3fn_decode_n(_p(q), _p(out), C.c_size_t(q.size))
+    lib().orc_e4m3fn_decode_n(_p(q), _p(out), C.c_size_t(q.size))
     return out
 
 
 def e4m3fn_encode(x) -> np.ndarray:
     x = _c(x, np.float32)
     out = np.empty(x.shape, np.uint8)
-    lib().rdb_e4m3fn_encode_n(_p(x), _p(out), C.c_size_t(x.size))
+    lib().orc_e4m3fn_encode_n(_p(x), _p(out), C.c_size_t(x.size))
     return out
 
 
@@ -75,7 +75,7 @@ def bf16_encode(x) -> np.ndarray:
     """fp32 -> bf16 bit patterns (uint16), round-to-nearest-even."""
     x = _c(x, np.float32)
     out = np.empty(x.shape, np.uint16)
-    lib().rdb_bf16_encode_n(_p(x), _p(out), C.c_size_t(x.size))
+    lib().orc_bf16_encode_n(_p(x), _p(out), C.c_size_t(x.size))
     return out
 
 
@@ -90,7 +90,7 @@ def quantize_per_tensor(x):
     x = _c(x, np.float32)
     q = np.empty(x.shape, np.uint8)
     s = C.c_float()
-    lib().rdb_quantize_per_tensor(_p(x), C.c_size_t(x.size), _p(q), C.byref(s))
+    lib().orc_quantize_per_tensor(_p(x), C.c_size_t(x.size), _p(q), C.byref(s))
     return q, np.float32(s.value)
 
 
@@ -100,7 +100,7 @@ def quantize_blocks128(x_bf16):
     assert x.size % 128 == 0
     q = np.empty(x.shape, np.uint8)
     s = np.empty(x.size // 128, np.float32)
-    lib().rdb_quantize_blocks128(_p(x), C.c_size_t(x.size), _p(q), _p(s))
+    lib().orc_quantize_blocks128(_p(x), C.c_size_t(x.size), _p(q), _p(s))
     return q, s
 
 
@@ -113,7 +113,7 @@ def gemm_fp8_bf16(A, B, scale_a, scale_b, ldb=None) -> np.ndarray:
     N = B.shape[0]
     ldb = B.shape[1] if ldb is None else ldb
     D = np.empty((M, N), np.uint16)
-    lib().rdb_gemm_fp8_bf16(_p(A), _p(B), C.c_float(scale_a), C.c_float(scale_b), _p(D),
+    lib().orc_gemm_fp8_bf16(_p(A), _p(B), C.c_float(scale_a), C.c_float(scale_b), _p(D),
                             C.c_int(M), C.c_int(N), C.c_int(K), C.c_int(ldb))
     return D
 
@@ -128,7 +128,7 @@ def gemm_fp8_f64(A, B, scale_a, scale_b, ldb=None):
     ldb = B.shape[1] if ldb is None else ldb
     D = np.empty((M, N), np.float64)
     mag = np.empty((M, N), np.float64)
-    lib().rdb_gemm_fp8_f64(_p(A), _p(B), C.c_float(scale_a), C.c_float(scale_b), _p(D), _p(mag),
+    lib().orc_gemm_fp8_f64(_p(A), _p(B), C.c_float(scale_a), C.c_float(scale_b), _p(D), _p(mag),
                            C.c_int(M), C.c_int(N), C.c_int(K), C.c_int(ldb))
     return D, mag
 
@@ -139,7 +139,7 @@ def gemm_fp8_f32(A, B) -> np.ndarray:
     M, K = A.shape
     N = B.shape[0]
     D = np.empty((M, N), np.float32)
-    lib().rdb_gemm_fp8_f32(_p(A), _p(B), _p(D), C.c_int(M), C.c_int(N), C.c_int(K))
+    lib().orc_gemm_fp8_f32(_p(A), _p(B), _p(D), C.c_int(M), C.c_int(N), C.c_int(K))
     return D
 
 
@@ -149,7 +149,7 @@ def tiled_sum_reduce(A, B) -> np.ndarray:
     B = _c(B, np.float32)
     b, m, n = A.shape
     D = np.empty((m, n), np.float32)
-    lib().rdb_tiled_sum_reduce(_p(A), _p(B), _p(D), C.c_int(b), C.c_int(m), C.c_int(n))
+    lib().orc_tiled_sum_reduce(_p(A), _p(B), _p(D), C.c_int(b), C.c_int(m), C.c_int(n))
     return D
 
 
@@ -162,7 +162,7 @@ def allreduce_fp8(xs_bf16):
     out = np.empty(n, np.uint16)
     q = np.empty((r, n), np.uint8)
     s = np.empty((r, n // 128), np.float32)
-    lib().rdb_allreduce_fp8(_p(xs), C.c_int(r), C.c_size_t(n), _p(out), _p(q), _p(s))
+    lib().orc_allreduce_fp8(_p(xs), C.c_int(r), C.c_size_t(n), _p(out), _p(q), _p(s))
     return out, q, s
 
 
@@ -171,7 +171,7 @@ def prune_2of4(W) -> np.ndarray:
     W = np.array(W, dtype=np.float32, order="C", copy=True)
     N, K = W.shape
     assert K % 4 == 0
-    lib().rdb_prune_2of4(_p(W), C.c_int(N), C.c_int(K))
+    lib().orc_prune_2of4(_p(W), C.c_int(N), C.c_int(K))
     return W
 
 
@@ -181,7 +181,7 @@ def compress_2of4(Wq):
     N, K = Wq.shape
     vals = np.empty((N, K // 2), np.uint8)
     meta = np.empty((N, K // 4), np.uint8)
-    bad = lib().rdb_compress_2of4(_p(Wq), C.c_int(N), C.c_int(K), _p(vals), _p(meta))
+    bad = lib().orc_compress_2of4(_p(Wq), C.c_int(N), C.c_int(K), _p(vals), _p(meta))
     return vals, meta, int(bad)
 
 
@@ -190,7 +190,7 @@ def expand_2of4(vals, meta) -> np.ndarray:
     meta = _c(meta, np.uint8)
     N, K4 = meta.shape
     Wq = np.empty((N, K4 * 4), np.uint8)
-    lib().rdb_expand_2of4(_p(vals), _p(meta), C.c_int(N), C.c_int(K4 * 4), _p(Wq))
+    lib().orc_expand_2of4(_p(vals), _p(meta), C.c_int(N), C.c_int(K4 * 4), _p(Wq))
     return Wq
 
 
@@ -199,5 +199,5 @@ def deltas(x, ref):
     x = _c(x, np.float32).ravel()
     ref = _c(ref, np.float32).ravel()
     mx, tot = C.c_float(), C.c_float()
-    lib().rdb_deltas(_p(x), _p(ref), C.c_size_t(x.size), C.byref(mx), C.byref(tot))
+    lib().orc_deltas(_p(x), _p(ref), C.c_size_t(x.size), C.byref(mx), C.byref(tot))
     return mx.value, tot.value

@@ -1,0 +1,12 @@
+// argv: b m n.
+#include "common.cuh"
+
+int main(int argc, char** argv) {
+    if (argc != 4) return 2;
+    const int b = atoi(argv[1]), m = atoi(argv[2]), n = atoi(argv[3]);
+    const size_t mn = static_cast<size_t>(m) * n;
+    auto hA = random_f32(b * mn), hB = random_f32(b * mn);
+    float *dA = to_device(hA), *dB = to_device(hB), *dD = device_zeros<float>(mn);
+    bench_protocol(20, 100, [&](int) { RDB_CHECK(rdb_tiled_sum_reduce(dA, dB, dD, b, m, n, nullptr)); });
+    return 0;
+}
