@@ -130,6 +130,28 @@ int rdb_dense_gemm_fp8(const uint8_t *A, const uint8_t *B, const float *scale_a,
  * D [M,N] OVERWRITTEN (async_gemm<float>, same citations). */
 int rdb_dense_gemm_fp8_f32(const uint8_t *A, const uint8_t *B, float *D, int M, int N, int K, void *stream);
 
+/* -------------------------------------------------------- 2:4 sparse GEMM
+ * D[M,N] = bf16( (A . W^T) * scale_a[0] * scale_b[0] ), M <= 256, K % 256 == 0,
+ * where W [N,K] has at most two non-zero bytes in every aligned group of four
+ * along K and is passed compressed: Wvals [N, K/2] (the kept bytes, in
+ * position order) and Wmeta (their 2-bit positions, rdb_sparse_meta_bytes(N,K)
+ * bytes in the layout rdb_sparse_pack_2of4 writes).  The reference's
+ * async_gemm_sparse (projects/async_gemm_sparse/sparse_k.cu:45-75) has the
+ * signature async_gemm<T>(A, B, D, m, n, k) and multiplies a DENSE B with the
+ * sparse instruction and fake indices; it has no compressed format, so the two
+ * extra operands are new. */
+int rdb_sparse_gemm_fp8(const uint8_t *A, const uint8_t *Wvals, const uint8_t *Wmeta, const float *scale_a,
+                        const float *scale_b, uint16_t *D, int M, int N, int K, void *stream);
+/* Same with the K split (1, 2 or 4 CTAs per cluster; 0 = automatic) chosen by the caller. */
+int rdb_sparse_gemm_fp8_tuned(const uint8_t *A, const uint8_t *Wvals, const uint8_t *Wmeta, const float *scale_a,
+                              const float *scale_b, uint16_t *D, int M, int N, int K, int split_k, void *stream);
+/* Host-side packer (no GPU): Wq [N,K] e4m3 bytes that already are 2:4 ->
+ * vals [N,K/2] and meta.  Returns RDB_INVALID_CONFIG if a group of four holds
+ * more than two non-zero bytes.  rdb_sparse_meta_bytes gives meta's size (0 for
+ * an unsupported shape). */
+size_t rdb_sparse_meta_bytes(int N, int K);
+int rdb_sparse_pack_2of4(const uint8_t *Wq, int N, int K, uint8_t *vals, uint8_t *meta);
+
 /* ---------------------------------------------------------- sum reduce
  * D[m,n] = sum over the batch of (A[i,m,n] + B[i,m,n]), fp32, summed in batch
  * order (bit-identical to the host loop).  A, B [b,m,n], D [m,n], any m, n;

@@ -1,0 +1,385 @@
+// 2:4 structured-sparse FP8 GEMM for sm_100a:
+//   D[M,N] = bf16( (A . W^T) * sa * sb ),  W [N,K] with two non-zeros in every aligned group of four along K.
+//
+// The reference's async_gemm_sparse project (projects/async_gemm_sparse/
+// sparse_k.cu:5-75, consumer.cu:29-162) issues the *sparse* MFMA with constant
+// fake indices as a trick to run a dense 8-row tile; it holds no pruning,
+// compression or metadata code.  This file is the real thing: the weights are
+// stored compressed (values [N,K/2] + 2-bit positions), halving the bytes that
+// must cross HBM, and multiplied with tcgen05.mma.sp kind::f8f6f4.
+//
+// The sparse operand must be the MMA's A operand, so the problem is computed
+// transposed ("swap-AB"): a CTA owns 128 weight rows (TMEM lanes), the padded
+// batch is the MMA N extent (TMEM columns).  Per 128-byte compressed K block
+// (256 logical K) a stage holds: the compressed values (128 x 128 B, TMA,
+// SWIZZLE_128B), two activation boxes (NB x 128 B each), and two 2 KiB metadata
+// atoms ([128 rows][16 B], bulk-copied), which the MMA thread moves into TMEM
+// with tcgen05.cp.128x128b before issuing four tcgen05.mma.sp (K = 64 each).
+// K may be split over a cluster of 2 or 4 CTAs (small batches); the partials are
+// exchanged through distributed shared memory with st.async and summed in rank
+// order.  Epilogue code is kept compact and cooperative (it runs once per CTA).
+#include <cuda_bf16.h>
+
+#include <cstring>
+
+#include "host_util.h"
+#include "ptx.cuh"
+
+namespace rdb {
+namespace sparse {
+
+constexpr int BM = 128;                 // weight rows per CTA (UMMA M)
+constexpr int BKC = 128;                // compressed K bytes per stage (256 logical K elements)
+constexpr int A_BYTES = BM * BKC;       // 16 KiB of compressed values
+constexpr int ATOM_BYTES = 2048;        // metadata atom: 128 rows x 16 B = 128 logical K
+constexpr int E_BYTES = 2 * ATOM_BYTES;
+constexpr int NUM_THREADS = 192;
+constexpr int MAX_STAGES = 8;
+constexpr int BAR_BYTES = 256;
+constexpr int SMEM_LIMIT = 232448;
+constexpr int TMEM_E_COL = 256;         // metadata columns start here: 8 per stage
+
+__host__ __device__ constexpr int stage_bytes(int NB) { return A_BYTES + 2 * NB * 128 + E_BYTES; }
+__host__ __device__ constexpr int red_bytes(int NB, int S) { return S > 1 ? BM * NB * 4 : 0; }   // [S][128/S rows][NB]
+__host__ __device__ constexpr int stg_bytes(int NB) { return BM * (NB + 4) * 4; }
+__host__ __device__ inline int smem_bytes(int NB, int S, int stages) {
+    int ring = stages * stage_bytes(NB);
+    if (ring < stg_bytes(NB)) ring = stg_bytes(NB);     // the staging tile reuses the drained ring
+    return 1024 + ring + red_bytes(NB, S) + BAR_BYTES;
+}
+
+struct Params {
+    __nv_bfloat16* D;
+    const uint8_t* meta;       // packed metadata: [N/128 tiles][K/128 atoms][128 rows][16 B]
+    const float* scale_a;
+    const float* scale_b;
+    int* status;
+    int M, N;
+    int num_kb;                // K / 256
+    int NB;                    // padded batch (UMMA N)
+    int nstages;
+    int ring_bytes;
+};
+
+// e4m3 x e4m3 -> f32, K-major operands, sparse A.
+__host__ __device__ constexpr uint32_t idesc_sparse(int umma_m, int umma_n) {
+    return (1u << 2) | (1u << 4) | (static_cast<uint32_t>(umma_n >> 3) << 17) | (static_cast<uint32_t>(umma_m >> 4) << 24);
+}
+
+// Shared-memory descriptor of one metadata atom: no swizzle, 8-row groups 128 B apart.
+__device__ __forceinline__ uint64_t smem_desc_meta(uint32_t addr) {
+    return static_cast<uint64_t>((addr & 0x3FFFFu) >> 4) | (static_cast<uint64_t>(128 >> 4) << 32) | (1ull << 46);
+}
+
+__device__ __forceinline__ void tmem_cp_128x128b(uint32_t taddr, uint64_t sdesc) {
+    asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+__device__ __forceinline__ void tc_mma_sp_f8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t tmem_e,
+                                             uint32_t idesc, bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %5, 0;\n\t"
+        "tcgen05.mma.sp.cta_group::1.kind::f8f6f4 [%0], %1, %2, [%3], %4, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(tmem_e), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
+        : "memory");
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+                 : "memory");
+}
+
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Params p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int S = gridDim.x, rank = blockIdx.x;      // cluster = K slices of one tile
+    const int tile = blockIdx.y, n0 = tile * BM;
+    const int NB = p.NB, nstages = p.nstages;
+    const int STAGE = stage_bytes(NB);
+    const int kb_begin = static_cast<int>((static_cast<long long>(p.num_kb) * rank) / S);
+    const int kb_end = static_cast<int>((static_cast<long long>(p.num_kb) * (rank + 1)) / S);
+    const int nkb = kb_end - kb_begin;
+
+    float* red = reinterpret_cast<float*>(smem + p.ring_bytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(red) + red_bytes(NB, S));
+    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + MAX_STAGES);
+    const uint32_t tmem_full = smem_u32(bars + 2 * MAX_STAGES), xbar = smem_u32(bars + 2 * MAX_STAGES + 1);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    const uint32_t stage0 = smem_u32(smem);
+    const int rows_per = BM / S;                      // S is 1, 2 or 4
+
+    if (threadIdx.x == 0) {
+        prefetch_tensormap(&tmW);
+        prefetch_tensormap(&tmX);
+        for (int s = 0; s < nstages; s++) {
+            mbar_init(full0 + 8 * s, 1);
+            mbar_init(empty0 + 8 * s, 1);
+        }
+        mbar_init(tmem_full, 1);
+        mbar_init(xbar, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        if (S > 1) mbar_arrive_expect_tx(xbar, static_cast<uint32_t>(S) * rows_per * NB * 4u);
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    if (S > 1) cluster_arrive_release();              // phase 1: "my barriers and buffers are live"
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
+            const uint8_t* meta_tile = p.meta + static_cast<size_t>(tile) * (2 * p.num_kb) * ATOM_BYTES;
+            for (int i = 0; i < nkb; i++) {
+                const int s = i % nstages;
+                const uint32_t ph = (i / nstages) & 1;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { *abort_flag = 1; report_timeout(p.status); break; }
+                const int kb = kb_begin + i;
+                const uint32_t dst = stage0 + s * STAGE, bar = full0 + 8 * s;
+                mbar_arrive_expect_tx(bar, STAGE);
+                tma_load_2d(dst, &tmW, kb * BKC, n0, bar, pol_w);
+                tma_load_2d(dst + A_BYTES, &tmX, kb * 256, 0, bar, pol_x);
+                tma_load_2d(dst + A_BYTES + NB * 128, &tmX, kb * 256 + 128, 0, bar, pol_x);
+                bulk_load(dst + A_BYTES + 2 * NB * 128, meta_tile + static_cast<size_t>(2 * kb) * ATOM_BYTES, E_BYTES, bar);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = idesc_sparse(BM, NB);
+            for (int i = 0; i < nkb; i++) {
+                const int s = i % nstages;
+                const uint32_t ph = (i / nstages) & 1;
+                if (!mbar_wait(full0 + 8 * s, ph)) { *abort_flag = 1; report_timeout(p.status); break; }
+                tc_fence_after_sync();
+                const uint32_t a = stage0 + s * STAGE, b = a + A_BYTES, e = b + 2 * NB * 128;
+                const uint32_t te = tmem_base + TMEM_E_COL + 8 * s;
+                tmem_cp_128x128b(te, smem_desc_meta(e));
+                tmem_cp_128x128b(te + 4, smem_desc_meta(e + ATOM_BYTES));
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    tc_mma_sp_f8(tmem_base, smem_desc_k128(a + 32 * j), smem_desc_k128(b + (j >> 1) * NB * 128 + (j & 1) * 64),
+                                 te + 2 * j, idesc, (i | j) != 0);
+                tc_commit(empty0 + 8 * s);
+            }
+            tc_commit(tmem_full);
+        }
+        __syncwarp();
+    }
+
+    // ---- epilogue: warps 2..5 move their TMEM lane quadrant (32 weight rows
+    // each) into the staging tile stg[row][NB] (pitch NB+4) in the drained ring.
+    float* stg = reinterpret_cast<float*>(smem);
+    const int pitch = NB + 4;
+    if (warp >= 2) {
+        bool ok = mbar_wait(tmem_full, 0);
+        if (!ok) { *abort_flag = 1; report_timeout(p.status); }
+        ok = ok && (*abort_flag == 0);
+        tc_fence_after_sync();
+        if (ok) {
+            const int quad = warp & 3;
+            float* row = stg + (quad * 32 + lane) * pitch;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+            for (int c0 = 0; c0 < NB; c0 += 16) {
+                float v[16];
+                tmem_ld16(taddr + c0, v);
+#pragma unroll
+                for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(row + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+        }
+    }
+    if (S > 1) cluster_wait_acquire();
+    __syncthreads();
+    const float sc = __ldg(p.scale_a) * __ldg(p.scale_b);
+
+    if (S == 1) {
+        if (*abort_flag == 0) {
+            // item = (batch row m, pair of weight rows): one bf16x2 store, coalesced along n
+            for (int item = threadIdx.x; item < p.M * (BM / 2); item += NUM_THREADS) {
+                const int m = item / (BM / 2), r = (item - m * (BM / 2)) * 2;
+                const int n = n0 + r;
+                if (n + 1 < p.N) {
+                    *reinterpret_cast<__nv_bfloat162*>(p.D + static_cast<size_t>(m) * p.N + n) =
+                        __floats2bfloat162_rn(stg[r * pitch + m] * sc, stg[(r + 1) * pitch + m] * sc);
+                } else if (n < p.N) {
+                    p.D[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(stg[r * pitch + m] * sc);
+                }
+            }
+        }
+    } else {
+        // push: item = (weight row, 4-column granule) -> the rank that owns the row
+        const int G = NB / 4;
+        for (int item = threadIdx.x; item < BM * G; item += NUM_THREADS) {
+            const int r = item / G, g = item - r * G;
+            const int owner = r / rows_per, rl = r - owner * rows_per;
+            const float4 v = *reinterpret_cast<const float4*>(stg + r * pitch + 4 * g);
+            const uint32_t dst = mapa_smem(smem_u32(red + (static_cast<size_t>(rank) * rows_per + rl) * NB + 4 * g), owner);
+            st_async_v4(dst, v.x, v.y, v.z, v.w, mapa_smem(xbar, owner));
+        }
+        if (!mbar_wait(xbar, 0)) { *abort_flag = 1; report_timeout(p.status); }
+        __syncthreads();
+        if (*abort_flag == 0) {
+            for (int item = threadIdx.x; item < p.M * (rows_per / 2); item += NUM_THREADS) {
+                const int m = item / (rows_per / 2), rl = (item - m * (rows_per / 2)) * 2;
+                float s0 = 0.f, s1 = 0.f;
+                for (int src = 0; src < S; src++) {                 // rank order
+                    s0 += red[(static_cast<size_t>(src) * rows_per + rl) * NB + m];
+                    s1 += red[(static_cast<size_t>(src) * rows_per + rl + 1) * NB + m];
+                }
+                const int n = n0 + rank * rows_per + rl;
+                if (n + 1 < p.N) {
+                    *reinterpret_cast<__nv_bfloat162*>(p.D + static_cast<size_t>(m) * p.N + n) = __floats2bfloat162_rn(s0 * sc, s1 * sc);
+                } else if (n < p.N) {
+                    p.D[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(s0 * sc);
+                }
+            }
+        }
+    }
+
+    if (*abort_flag != 0) {
+        for (int i = 0; i < 64; i++) __nanosleep(2000);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+}
+
+static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* sa, const float* sb, uint16_t* D,
+               int M, int N, int K, int split_k_hint, cudaStream_t stream) {
+    if (M < 1 || N < 1 || K < 1) return RDB_BAD_SHAPE;
+    if (M > 256) return RDB_M_ABOVE_WARPTILE_M;
+    if (N % 2 != 0) return RDB_N_NOT_EVEN;
+    if (K % 256 != 0) return RDB_K_NOT_DIVISIBLE_BY_WARPTILE_K;
+    if (!aligned16(A) || !aligned16(Wvals) || !aligned16(Wmeta) || (reinterpret_cast<uintptr_t>(D) & 3u)) return RDB_BAD_ALIGNMENT;
+    if (split_k_hint != 0 && split_k_hint != 1 && split_k_hint != 2 && split_k_hint != 4) return RDB_INVALID_CONFIG;
+    int err = 0;
+    DeviceInfo* info = device_info(&err);
+    if (!info) return err;
+    const int NB = (M + 15) / 16 * 16;
+    const int tiles = (N + BM - 1) / BM;
+    const int num_kb = K / 256;
+    int S = split_k_hint;
+    if (S == 0) {
+        // resident clusters of 2 / 4 CTAs on a 148-SM part: 74 / 33 (one per SM)
+        S = 1;
+        if (NB <= 64) {
+            if (tiles * 4 <= info->sm_count && tiles <= 33 * info->sm_count / 148) S = 4;
+            else if (tiles * 2 <= info->sm_count) S = 2;
+        }
+    }
+    while (S > 1 && (S > num_kb || NB > 64)) S /= 2;
+    int stages = (200 * 1024 - red_bytes(NB, S)) / stage_bytes(NB);
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    const int kb_per = (num_kb + S - 1) / S;
+    if (stages > kb_per) stages = kb_per;
+    if (stages < 1) stages = 1;
+    while (stages > 1 && smem_bytes(NB, S, stages) > SMEM_LIMIT) stages--;
+    if (smem_bytes(NB, S, stages) > SMEM_LIMIT) return RDB_SIZE_ABOVE_LIMIT;
+
+    static bool attr_set[kMaxDevices] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!attr_set[dev]) {
+        if (cudaFuncSetAttribute(sparse_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess)
+            return RDB_CUDA_ERROR;
+        attr_set[dev] = true;
+    }
+    CUtensorMap tmW, tmX;
+    int r = make_tmap_2d(&tmW, Wvals, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, BKC, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != RDB_SUCCESS) return r;
+    r = make_tmap_2d(&tmX, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, 128, NB, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (r != RDB_SUCCESS) return r;
+    Params p;
+    p.D = reinterpret_cast<__nv_bfloat16*>(D);
+    p.meta = Wmeta;
+    p.scale_a = sa;
+    p.scale_b = sb;
+    p.status = info->status_dev;
+    p.M = M;
+    p.N = N;
+    p.num_kb = num_kb;
+    p.NB = NB;
+    p.nstages = stages;
+    int ring = stages * stage_bytes(NB);
+    if (ring < stg_bytes(NB)) ring = stg_bytes(NB);
+    p.ring_bytes = ring;
+
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(S, tiles, 1);
+    cfg.blockDim = dim3(NUM_THREADS, 1, 1);
+    cfg.dynamicSmemBytes = smem_bytes(NB, S, stages);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = S;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, sparse_gemm_kernel, tmW, tmX, p) == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
+}
+
+}  // namespace sparse
+}  // namespace rdb
+
+extern "C" {
+
+size_t rdb_sparse_meta_bytes(int N, int K) {
+    if (N < 1 || K < 1 || K % 256 != 0) return 0;
+    return static_cast<size_t>((N + 127) / 128) * (K / 128) * rdb::sparse::ATOM_BYTES;
+}
+
+// Host-side packer (no GPU involved): compresses a 2:4 matrix of e4m3 bytes.
+int rdb_sparse_pack_2of4(const uint8_t* Wq, int N, int K, uint8_t* vals, uint8_t* meta) {
+    if (N < 1 || K < 1 || K % 256 != 0) return RDB_BAD_SHAPE;
+    const int tiles = (N + 127) / 128, atoms = K / 128;
+    memset(meta, 0, static_cast<size_t>(tiles) * atoms * rdb::sparse::ATOM_BYTES);
+    for (int n = 0; n < N; n++) {
+        const uint8_t* w = Wq + static_cast<size_t>(n) * K;
+        uint8_t* v = vals + static_cast<size_t>(n) * (K / 2);
+        uint8_t* mrow = meta + (static_cast<size_t>(n / 128) * atoms * 128 + (n % 128)) * 16;
+        for (int c = 0; c < K / 4; c++) {
+            int idx[2], cnt = 0;
+            for (int i = 0; i < 4; i++) {
+                if ((w[4 * c + i] & 0x7F) != 0) {          // +0 and -0 both count as zero
+                    if (cnt == 2) return RDB_INVALID_CONFIG;  // more than two non-zeros: not a 2:4 matrix
+                    idx[cnt++] = i;
+                }
+            }
+            // pad with the lowest unused positions so that the pair stays strictly ascending
+            for (int i = 0; i < 4 && cnt < 2; i++)
+                if (cnt == 0 || idx[0] != i) idx[cnt++] = i;
+            if (idx[0] > idx[1]) { const int t = idx[0]; idx[0] = idx[1]; idx[1] = t; }
+            v[2 * c] = w[4 * c + idx[0]];
+            v[2 * c + 1] = w[4 * c + idx[1]];
+            const uint8_t nib = static_cast<uint8_t>(idx[0] | (idx[1] << 2));
+            // chunk c of the row lives in atom c/32, byte (c%32)/2, low nibble first
+            uint8_t* dst = mrow + static_cast<size_t>(c / 32) * 128 * 16 + (c % 32) / 2;
+            *dst |= (c & 1) ? static_cast<uint8_t>(nib << 4) : nib;
+        }
+    }
+    return RDB_SUCCESS;
+}
+
+int rdb_sparse_gemm_fp8(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* scale_a,
+                        const float* scale_b, uint16_t* D, int M, int N, int K, void* stream) {
+    return rdb::sparse::run(A, Wvals, Wmeta, scale_a, scale_b, D, M, N, K, 0, static_cast<cudaStream_t>(stream));
+}
+
+int rdb_sparse_gemm_fp8_tuned(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* scale_a,
+                              const float* scale_b, uint16_t* D, int M, int N, int K, int split_k, void* stream) {
+    return rdb::sparse::run(A, Wvals, Wmeta, scale_a, scale_b, D, M, N, K, split_k, static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,59 @@
+"""Host side of the 2:4 structured-sparse FP8 GEMM.
+
+The reference's ``async_gemm_sparse`` (projects/async_gemm_sparse/ in the
+reference project) keeps the dense launcher signature ``async_gemm(A, B, D, m,
+n, k)`` and contains no pruning or compression; the pruning rule, the
+compressed format and the packer here implement the configuration text: keep
+the two largest magnitudes of every aligned group of four along K (ties: the
+lowest index), quantise per tensor, store the kept bytes plus 2-bit positions.
+"""
+from __future__ import annotations
+
+import torch
+
+from ._lib import check, lib
+
+
+def prune_2of4(W: torch.Tensor) -> torch.Tensor:
+    """Zero all but the two largest-magnitude entries of each group of four
+    along the last dimension (ties: lowest index).  CPU or GPU tensor."""
+    assert W.shape[-1] % 4 == 0
+    g = W.reshape(-1, 4)
+    a = g.abs().float()
+    # stable descending order keeps the lower index on ties
+    order = torch.argsort(a, dim=1, descending=True, stable=True)
+    keep = torch.zeros_like(a, dtype=torch.bool)
+    keep.scatter_(1, order[:, :2], True)
+    return torch.where(keep, g, torch.zeros_like(g)).reshape(W.shape)
+
+
+def pack_2of4(Wq: torch.Tensor):
+    """Wq: [N,K] uint8 e4m3 bytes that are already 2:4 (CPU).  Returns
+    (vals [N,K/2] uint8, meta uint8) in the layout the kernel consumes."""
+    assert Wq.dtype == torch.uint8 and Wq.dim() == 2 and not Wq.is_cuda
+    Wq = Wq.contiguous()
+    N, K = Wq.shape
+    nbytes = int(lib().rdb_sparse_meta_bytes(N, K))
+    if nbytes == 0:
+        raise ValueError("K must be a multiple of 256")
+    vals = torch.empty((N, K // 2), dtype=torch.uint8)
+    meta = torch.empty(nbytes, dtype=torch.uint8)
+    check(lib().rdb_sparse_pack_2of4(Wq.data_ptr(), N, K, vals.data_ptr(), meta.data_ptr()), "rdb_sparse_pack_2of4")
+    return vals, meta
+
+
+def sparse_gemm_fp8(A: torch.Tensor, vals: torch.Tensor, meta: torch.Tensor, scale_a: torch.Tensor,
+                    scale_b: torch.Tensor, out: torch.Tensor | None = None, split_k: int = 0) -> torch.Tensor:
+    """D[M,N] = bf16((A . W^T) * scale_a * scale_b) with W given compressed."""
+    assert A.is_cuda and vals.is_cuda and meta.is_cuda and A.is_contiguous() and vals.is_contiguous()
+    A = A if A.dtype == torch.uint8 else A.view(torch.uint8)
+    M, K = A.shape
+    N = vals.shape[0]
+    assert vals.shape[1] * 2 == K
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
+    with torch.cuda.device(A.device):
+        check(lib().rdb_sparse_gemm_fp8_tuned(A.data_ptr(), vals.data_ptr(), meta.data_ptr(), scale_a.data_ptr(),
+                                              scale_b.data_ptr(), out.data_ptr(), M, N, K, split_k,
+                                              torch.cuda.current_stream(A.device).cuda_stream), "rdb_sparse_gemm_fp8")
+    return out
