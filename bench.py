@@ -406,6 +406,143 @@ def bench_allreduce(torch, dist, R, dev, rank, world):
     return out
 
 
+# ------------------------------------------------------- secondary suites
+def _graph_time(torch, stream, fn, iters, reps=3):
+    """Average device time (us) of fn(i) over a replayed CUDA graph of `iters` calls."""
+    with torch.cuda.stream(stream):
+        for i in range(2):
+            fn(i)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            for i in range(iters):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(reps):
+            g.replay()
+        b.record(stream)
+        torch.cuda.synchronize()
+    return a.elapsed_time(b) * 1e3 / (reps * iters)
+
+
+def run_suite(args):
+    """Measured lines for the other paths of the scope table (one JSON line per
+    invocation): dense GEMM (config 2, row-sharded over the ranks), 2:4 sparse
+    GEMM (config 3), tiled_sum_reduce.  Not the headline metric."""
+    import torch
+    import torch.distributed as dist
+
+    import rocm_dev_b200 as R
+    from rocm_dev_b200 import quant
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        dist.init_process_group("nccl", device_id=dev)
+    stream = torch.cuda.Stream(device=dev)
+    one = torch.ones(1, device=dev)
+    peak_hbm, kind = measured_peak()
+    out = {"suite": args.suite, "n_gpus": world, "data": "synthetic", "peak_kind": f"of {kind}"}
+
+    def maxrank(us):
+        if world == 1:
+            return us
+        t = torch.tensor([us], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    if args.suite == "dense":
+        # config 2: M = N = K, the M rows of A and D split over the ranks, B replicated, no communication
+        cases = {}
+        for n in (4096, 8192, 16384):
+            m_local = n // world
+            g = torch.Generator(device=dev).manual_seed(n + rank)
+            A = torch.randint(0, 0x78, (m_local, n), generator=g, dtype=torch.uint8, device=dev)
+            B = torch.randint(0, 0x78, (n, n), generator=g, dtype=torch.uint8, device=dev)
+            D = torch.empty((m_local, n), dtype=torch.bfloat16, device=dev)
+            iters = 20 if n < 16384 else 4
+            if world > 1:
+                dist.barrier()
+            us = maxrank(_graph_time(torch, stream, lambda i: R.dense_gemm_fp8(A, B, one, one, out=D), iters))
+            lib_us = None
+            try:
+                a8, b8 = A.view(torch.float8_e4m3fn), B.view(torch.float8_e4m3fn).t()
+                lib_us = maxrank(_graph_time(torch, stream, lambda i: torch._scaled_mm(a8, b8, scale_a=one, scale_b=one,
+                                                                                      out_dtype=torch.bfloat16), iters))
+            except Exception:  # noqa: BLE001
+                pass
+            tf = 2.0 * n * n * n / us / 1e6
+            cases[str(n)] = {"us": round(us, 1), "tflops": round(tf, 1), "frac_of_4500_nominal": round(tf / 4500, 3),
+                             "cublaslt_fp8_tflops": round(2.0 * n ** 3 / lib_us / 1e6, 1) if lib_us else None}
+            del A, B, D
+        out.update({"metric": "dense FP8 GEMM TFLOP/s (whole job)", "unit": "TFLOP/s", "scaling": "strong",
+                    "config": {"workload": "configs[2]: M=N=K, rows of A/D sharded over ranks, no communication"},
+                    "roofline": {"bound": "tensor", "peak": 4500.0, "unit": "TFLOP/s",
+                                 "peak_kind": "nominal dense FP8; cuBLASLt FP8 on the same box listed per case"},
+                    "cases": cases})
+    elif args.suite == "sparse":
+        N = K = 8192
+        copies = 3
+        g = torch.Generator().manual_seed(0)
+        dense_w, packed = [], []
+        for c in range(copies):
+            W = (torch.randn((N, K), generator=g) * 0.02).bfloat16()
+            Wq, _ = quant.quantize_per_tensor(R.prune_2of4(W))
+            v, m = R.pack_2of4(Wq)
+            dense_w.append(Wq.to(dev))
+            packed.append((v.to(dev), m.to(dev)))
+        cases = {}
+        for M in (16, 64, 256):
+            A = torch.randint(0, 0x78, (M, K), dtype=torch.uint8, device=dev)
+            D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+            sp = _graph_time(torch, stream, lambda i: R.sparse_gemm_fp8(A, packed[i % copies][0], packed[i % copies][1],
+                                                                         one, one, out=D), 30)
+            de = _graph_time(torch, stream, lambda i: R.dense_gemm_fp8(A, dense_w[i % copies], one, one, out=D), 30)
+            sk = _graph_time(torch, stream, lambda i: R.skinny_gemm_fp8(A, dense_w[i % copies], one, one, out=D), 30) \
+                if M <= 32 else None
+            by = N * K // 2 + N * K // 8 + M * K + 2 * M * N
+            best_dense = min(x for x in (de, sk) if x)
+            cases[f"M{M}"] = {"sparse_us": round(sp, 2), "dense_gemm_us": round(de, 2),
+                              "skinny_us": round(sk, 2) if sk else None, "speedup_vs_best_dense": round(best_dense / sp, 3),
+                              "algorithmic_bytes": by, "gbs": round(by / sp / 1e3, 1),
+                              "frac_of_hbm": round(by / sp / 1e3 / peak_hbm, 3),
+                              "dense_equivalent_tflops": round(2.0 * M * N * K / sp / 1e6, 1)}
+        out.update({"metric": "2:4 sparse FP8 GEMM time vs own dense kernels", "unit": "us",
+                    "config": {"workload": "configs[3]: N=K=8192, M in {16,64,256}, 3 weight copies rotate (L2-cold)"},
+                    "roofline": {"bound": "hbm", "peak": peak_hbm, "unit": "GB/s"}, "cases": cases})
+    elif args.suite == "reduce":
+        cases = {}
+        for (b, m, n) in ((8, 4096, 4096), (32, 2048, 2048), (64, 512, 512)):
+            A = torch.rand((b, m, n), device=dev)
+            B = torch.rand((b, m, n), device=dev)
+            D = torch.empty((m, n), device=dev)
+            us = _graph_time(torch, stream, lambda i: R.tiled_sum_reduce(A, B, D, b, m, n), 10)
+            by = 8 * b * m * n + 4 * m * n
+            cases[f"{b}x{m}x{n}"] = {"us": round(us, 1), "gbs": round(by / us / 1e3, 1),
+                                     "frac": round(by / us / 1e3 / peak_hbm, 3)}
+        out.update({"metric": "tiled_sum_reduce HBM GB/s", "unit": "GB/s",
+                    "roofline": {"bound": "hbm", "peak": peak_hbm, "unit": "GB/s"}, "cases": cases})
+    elif args.suite == "allreduce":
+        if world < 2:
+            raise SystemExit("--suite allreduce needs torchrun with at least 2 ranks")
+        out.update({"metric": "FP8-encoded allreduce busBW vs NCCL bf16", "unit": "GB/s",
+                    "config": {"workload": "configs[4]: bf16 [T, 8192], T in {1,16,128,1024,4096}"},
+                    "allreduce": bench_allreduce(torch, dist, R, dev, rank, world)})
+    if R.lib().rdb_device_status() != 0:
+        out["error"] = "device status word reports a timed-out wait"
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -417,9 +554,13 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-allreduce", action="store_true")
+    ap.add_argument("--suite", default="", choices=["", "dense", "sparse", "reduce", "allreduce"],
+                    help="measure one of the other paths instead of the headline sweep")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.suite:
+        run_suite(args)
     else:
         run_gpu(args)
 
