@@ -219,6 +219,15 @@ int rdb_ar_phase(void *ctx, int phase, int epoch, const uint16_t *x, uint16_t *o
  * vector (n a multiple of 128), bit-exact with the definition above. */
 int rdb_quantize_blocks128(const uint16_t *x, uint8_t *q, float *scales, size_t n, void *stream);
 
+/* Diagnostic for the encoder's division: for each of `count` fp32 divisors
+ * (device array) and every bf16 bit pattern x a block with that scale can hold
+ * (|x| <= 512 * divisor, NaN included) compares the encoder's quotient with
+ * the IEEE quotient x / divisor.  Adds to mismatches[0] (device, two uint64
+ * zeroed by the caller) the number of differing e4m3 encodings - expected 0 -
+ * and to mismatches[1] the number of differing fp32 quotients of magnitude
+ * >= 2^-12 - expected 0 too.  No counterpart in the reference. */
+int rdb_debug_division_mismatches(const float *divisors, int count, unsigned long long *mismatches, void *stream);
+
 /* rdb_globs_n for callers that must not allocate device memory while they
  * run - a host application that owns all GPU memory and gives its plugins a
  * fixed arena, or a latency-critical loop where a device allocation (it

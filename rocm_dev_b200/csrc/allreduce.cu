@@ -109,39 +109,92 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
     return v;
 }
 
-// Encodes 16 consecutive elements held by this lane; the 8 lanes that share a
-// 128-element block agree on its scale.  Returns the 16 encoded bytes.
-__device__ __forceinline__ uint4 encode16(const uint4 lo, const uint4 hi, bool valid, float& scale_out) {
-    float v[16];
-    const uint32_t w[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+// x / s rounded to nearest, for a divisor shared by a whole block.  With inv =
+// RN(1/s), q0 = RN(x*inv), r = x - q0*s (exact, one FMA) and q = RN(q0 + r*inv)
+// the result equals the IEEE quotient (Markstein's correction step) whenever
+// the quotient neither overflows nor goes subnormal - and inside a block
+// |x| <= amax = 448 s, so |x/s| <= 448, while quotients below 2^-10 encode to
+// zero either way.  Three FMA-class instructions replace a full division,
+// which had made the encoder compute-bound.  `fast` is decided once per block:
+// divisors that are non-finite, tiny, huge or have an all-ones significand take
+// the IEEE division.  NaN elements stay NaN on both paths.
+struct BlockDivisor {
+    float s, inv;
+    bool fast;
+    __device__ __forceinline__ void set(float scale) {
+        s = scale;
+        const uint32_t u = __float_as_uint(scale);
+        const uint32_t e = (u >> 23) & 0xFF;
+        // 2^-80 <= s < 2^100: for every quotient that can reach the e4m3 grid (|q| >= 2^-12)
+        // the residual x - q0*s is then a normal number, hence exact
+        fast = (e > 46) && (e < 227) && ((u & 0x7FFFFFu) != 0x7FFFFFu);
+        inv = __frcp_rn(scale);
+    }
+    __device__ __forceinline__ float div_fast(float x) const {
+        const float q0 = __fmul_rn(x, inv);
+        const float r = __fmaf_rn(-q0, s, x);
+        return copysignf(__fmaf_rn(r, inv, q0), x);      // s > 0; keeps the sign of a zero quotient
+    }
+    // 8 quotients of one lane
+    __device__ __forceinline__ void div8(const float* x, float* q) const {
+        if (fast) {
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        v[2 * i] = valid ? __uint_as_float(w[i] << 16) : 0.0f;
-        v[2 * i + 1] = valid ? __uint_as_float(w[i] & 0xFFFF0000u) : 0.0f;
+            for (int i = 0; i < 8; i++) q[i] = div_fast(x[i]);
+        } else {
+#pragma unroll 1
+            for (int i = 0; i < 8; i++) q[i] = __fdiv_rn(x[i], s);
+        }
+    }
+};
+
+// amax / 448 rounded to nearest: the same correction step with the constant
+// divisor 448 (its reciprocal is rounded at compile time); amax below 2^-100
+// takes the IEEE division.
+__device__ __forceinline__ float block_scale(float amax) {
+    if (!(amax > 0.0f)) return 1.0f;
+    if (amax < 7.888609e-31f || !(amax < 3.0e38f)) return __fdiv_rn(amax, 448.0f);
+    constexpr float inv448 = 1.0f / 448.0f;
+    const float q0 = __fmul_rn(amax, inv448);
+    const float r = __fmaf_rn(-q0, 448.0f, amax);
+    return __fmaf_rn(r, inv448, q0);
+}
+
+// Encodes 8 consecutive bf16 elements (one uint4) held by this lane; the 16
+// lanes that share a 128-element block agree on its scale.  Elements beyond
+// the end of the vector are passed as zeros.  Returns 8 bytes.
+__device__ __forceinline__ uint2 encode8(const uint4 in, float& scale_out) {
+    float v[8];
+    const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        v[2 * i] = __uint_as_float(w[i] << 16);
+        v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
     }
     float amax = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 16; i++) amax = fmaxf(amax, fabsf(v[i]));
+    for (int i = 0; i < 8; i++) amax = fmaxf(amax, fabsf(v[i]));
 #pragma unroll
-    for (int o = 1; o < 8; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-    const float s = amax > 0.0f ? __fdiv_rn(amax, 448.0f) : 1.0f;
+    for (int o = 1; o < 16; o <<= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    const float s = block_scale(amax);
     scale_out = s;
-    uint32_t q[4];
+    BlockDivisor d;
+    d.set(s);
+    float t[8];
+    d.div8(v, t);
+    uint32_t q[2];
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
-        const __nv_fp8x2_storage_t a =
-            __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[4 * i], s), __fdiv_rn(v[4 * i + 1], s)), __NV_SATFINITE, __NV_E4M3);
-        const __nv_fp8x2_storage_t b =
-            __nv_cvt_float2_to_fp8x2(make_float2(__fdiv_rn(v[4 * i + 2], s), __fdiv_rn(v[4 * i + 3], s)), __NV_SATFINITE, __NV_E4M3);
+    for (int i = 0; i < 2; i++) {
+        const __nv_fp8x2_storage_t a = __nv_cvt_float2_to_fp8x2(make_float2(t[4 * i], t[4 * i + 1]), __NV_SATFINITE, __NV_E4M3);
+        const __nv_fp8x2_storage_t b = __nv_cvt_float2_to_fp8x2(make_float2(t[4 * i + 2], t[4 * i + 3]), __NV_SATFINITE, __NV_E4M3);
         q[i] = static_cast<uint32_t>(a) | (static_cast<uint32_t>(b) << 16);
     }
-    return make_uint4(q[0], q[1], q[2], q[3]);
+    return make_uint2(q[0], q[1]);
 }
 
-__device__ __forceinline__ void decode16(const uint4 q, float* v) {
-    const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+__device__ __forceinline__ void decode8(const uint2 q, float* v) {
+    const uint32_t w[2] = {q.x, q.y};
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < 2; i++) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const __half2_raw r = __nv_cvt_fp8x2_to_halfraw2(static_cast<__nv_fp8x2_storage_t>((w[i] >> (16 * h)) & 0xFFFFu), __NV_E4M3);
@@ -152,6 +205,13 @@ __device__ __forceinline__ void decode16(const uint4 q, float* v) {
         }
     }
 }
+
+// Work item of every kernel below: one warp per 512-element group, handled as
+// two halves of 256 elements; in half h lane l owns elements [256 h + 8 l,
+// 256 h + 8 l + 8).  Every load and store instruction of a warp therefore
+// touches one contiguous run (512 B of bf16, 256 B of fp8): full sectors and
+// full NVLink packets.  Block b of the group (128 elements) is lanes 0-15
+// (b even) or 16-31 (b odd) of half b / 2.
 
 // Called by every block at the end of a producing phase: the last block of the
 // grid to get here (counted in a word of the own workspace, after a system-wide
@@ -198,25 +258,25 @@ __device__ __forceinline__ bool wait_flags(const KParams& p, int which) {
 }
 
 // ------------------------------------------------------------------ phase 1
-// One warp per 512-element group: lane l holds elements [16 l, 16 l + 16).
 __global__ void __launch_bounds__(kThreads) ar_push_kernel(const KParams p) {
     const int lane = threadIdx.x & 31;
     const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
     const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
     for (size_t g = warp; g < p.groups; g += nwarps) {
-        const size_t e0 = g * kGroup + static_cast<size_t>(lane) * 16;
-        const bool valid = e0 < p.n;            // n is a multiple of 128, so validity is per 128-block
-        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-        if (valid) {
-            const uint4* src = reinterpret_cast<const uint4*>(p.x + e0);
-            lo = __ldg(src);
-            hi = __ldg(src + 1);
+        const size_t e0 = g * kGroup + static_cast<size_t>(lane) * 8;
+        uint4 in[2];
+        bool valid[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {                 // both loads in flight before any arithmetic
+            valid[h] = e0 + 256 * h < p.n;            // n is a multiple of 128: validity is uniform per block
+            in[h] = valid[h] ? __ldg(reinterpret_cast<const uint4*>(p.x + e0 + 256 * h)) : make_uint4(0, 0, 0, 0);
         }
-        float s;
-        const uint4 q = encode16(lo, hi, valid, s);
-        // the four block scales of the group, gathered on lane 0
-        const float s1 = __shfl_sync(0xffffffffu, s, 8), s2 = __shfl_sync(0xffffffffu, s, 16),
-                    s3 = __shfl_sync(0xffffffffu, s, 24);
+        uint2 q[2];
+        float s[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) q[h] = encode8(in[h], s[h]);
+        // the four block scales of the group: (half 0: lanes 0, 16), (half 1: lanes 0, 16)
+        const float s1 = __shfl_sync(0xffffffffu, s[0], 16), s3 = __shfl_sync(0xffffffffu, s[1], 16);
         int first, last;
         size_t slot_g;
         if (p.one_shot) { first = 0; last = p.world - 1; slot_g = g; }
@@ -230,11 +290,12 @@ __global__ void __launch_bounds__(kThreads) ar_push_kernel(const KParams p) {
         const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + p.rank) * p.L.slot_groups + slot_g;
         for (int peer = first; peer <= last; peer++) {
             uint8_t* base = p.ws[peer];
-            uint4* dq = reinterpret_cast<uint4*>(base + p.L.off_q + slot * kGroup) + lane;
-            *dq = q;
+            uint2* dq = reinterpret_cast<uint2*>(base + p.L.off_q + slot * kGroup) + lane;
+            dq[0] = q[0];
+            dq[32] = q[1];
             if (lane == 0) {
                 float4* ds = reinterpret_cast<float4*>(base + p.L.off_s) + slot;
-                *ds = make_float4(s, s1, s2, s3);
+                *ds = make_float4(s[0], s1, s[1], s3);
             }
         }
     }
@@ -252,36 +313,41 @@ __global__ void __launch_bounds__(kThreads) ar_reduce_kernel(const KParams p) {
     const uint8_t* mine = p.ws[p.rank];
     for (size_t g = gb + warp; arrived && g < ge; g += nwarps) {
         const size_t slot_g = g - gb;
-        float acc[16];
+        float acc[2][8];
 #pragma unroll
-        for (int i = 0; i < 16; i++) acc[i] = 0.0f;
+        for (int h = 0; h < 2; h++)
+#pragma unroll
+            for (int i = 0; i < 8; i++) acc[h][i] = 0.0f;
         for (int r = 0; r < p.world; r++) {
             const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + r) * p.L.slot_groups + slot_g;
-            const uint4 q = __ldcg(reinterpret_cast<const uint4*>(mine + p.L.off_q + slot * kGroup) + lane);
-            const float s = __ldcg(reinterpret_cast<const float*>(mine + p.L.off_s) + slot * 4 + (lane >> 3));
-            float v[16];
-            decode16(q, v);
+            const uint2* src = reinterpret_cast<const uint2*>(mine + p.L.off_q + slot * kGroup) + lane;
+            const uint2 q0 = __ldcg(src), q1 = __ldcg(src + 32);
+            const float* sc = reinterpret_cast<const float*>(mine + p.L.off_s) + slot * 4 + (lane >> 4);
+            const float s0 = __ldcg(sc), s1 = __ldcg(sc + 2);
+            float v[8];
+            decode8(q0, v);
 #pragma unroll
-            for (int i = 0; i < 16; i++) acc[i] = __fadd_rn(acc[i], __fmul_rn(v[i], s));   // product and sum rounded separately
-        }
-        uint32_t o[8];
+            for (int i = 0; i < 8; i++) acc[0][i] = __fadd_rn(acc[0][i], __fmul_rn(v[i], s0));   // product and sum rounded separately
+            decode8(q1, v);
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const __nv_bfloat162 b = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-            o[i] = *reinterpret_cast<const uint32_t*>(&b);
+            for (int i = 0; i < 8; i++) acc[1][i] = __fadd_rn(acc[1][i], __fmul_rn(v[i], s1));
         }
-        const size_t e0 = g * kGroup + static_cast<size_t>(lane) * 16;
-        if (e0 >= p.n) continue;
-        const uint4 lo = make_uint4(o[0], o[1], o[2], o[3]), hi = make_uint4(o[4], o[5], o[6], o[7]);
-        if (p.one_shot) {
-            uint4* d = reinterpret_cast<uint4*>(p.out + e0);
-            d[0] = lo;
-            d[1] = hi;
-        } else {
-            for (int peer = 0; peer < p.world; peer++) {
-                uint4* d = reinterpret_cast<uint4*>(p.ws[peer] + p.L.off_gather + e0 * 2);
-                d[0] = lo;
-                d[1] = hi;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const size_t e0 = g * kGroup + 256 * h + static_cast<size_t>(lane) * 8;
+            if (e0 >= p.n) continue;
+            uint32_t o[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const __nv_bfloat162 b = __floats2bfloat162_rn(acc[h][2 * i], acc[h][2 * i + 1]);
+                o[i] = *reinterpret_cast<const uint32_t*>(&b);
+            }
+            const uint4 val = make_uint4(o[0], o[1], o[2], o[3]);
+            if (p.one_shot) {
+                *reinterpret_cast<uint4*>(p.out + e0) = val;
+            } else {
+                for (int peer = 0; peer < p.world; peer++)
+                    *reinterpret_cast<uint4*>(p.ws[peer] + p.L.off_gather + e0 * 2) = val;
             }
         }
     }
@@ -308,25 +374,51 @@ __global__ void __launch_bounds__(kThreads) quantize_blocks128_kernel(const __nv
     const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
     const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
     for (size_t g = warp; g < groups; g += nwarps) {
-        const size_t e0 = g * kGroup + static_cast<size_t>(lane) * 16;
-        const bool valid = e0 < n;
-        uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
-        if (valid) {
-            lo = __ldg(reinterpret_cast<const uint4*>(x + e0));
-            hi = __ldg(reinterpret_cast<const uint4*>(x + e0) + 1);
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const size_t e0 = g * kGroup + 256 * h + static_cast<size_t>(lane) * 8;
+            const bool valid = e0 < n;
+            const uint4 in = valid ? __ldg(reinterpret_cast<const uint4*>(x + e0)) : make_uint4(0, 0, 0, 0);
+            float s;
+            const uint2 enc = encode8(in, s);
+            if (valid) {
+                *reinterpret_cast<uint2*>(q + e0) = enc;
+                if ((lane & 15) == 0) scales[e0 / 128] = s;
+            }
         }
-        float s;
-        const uint4 enc = encode16(lo, hi, valid, s);
-        if (valid) {
-            *reinterpret_cast<uint4*>(q + e0) = enc;
-            if ((lane & 7) == 0) scales[e0 / 128] = s;
+    }
+}
+
+// Diagnostic: for each divisor s[i] and every bf16 bit pattern x that a block
+// with that scale can hold (|x| <= 512 s, NaN included) compares the encoder's
+// quotient with the IEEE quotient x / s[i]: mismatches[0] counts differing
+// e4m3 bytes, mismatches[1] differing fp32 quotients among those of magnitude
+// >= 2^-12 (smaller ones encode to zero whatever their last bit).  Both must be 0.
+__global__ void div_check_kernel(const float* __restrict__ s, int ns, unsigned long long* mismatches) {
+    for (int i = blockIdx.x; i < ns; i += gridDim.x) {
+        BlockDivisor d;
+        d.set(s[i]);
+        unsigned bad8 = 0, bad32 = 0;
+        for (unsigned b = threadIdx.x; b < 65536u; b += blockDim.x) {
+            const float x = __uint_as_float(b << 16);
+            if (fabsf(x) > 512.0f * s[i]) continue;         // not reachable inside a block (also drops inf)
+            float xs[8] = {x, x, x, x, x, x, x, x}, q[8];
+            d.div8(xs, q);
+            const float a = q[0], e = __fdiv_rn(x, s[i]);
+            const unsigned ca = __nv_cvt_float2_to_fp8x2(make_float2(a, a), __NV_SATFINITE, __NV_E4M3) & 0xFF;
+            const unsigned ce = __nv_cvt_float2_to_fp8x2(make_float2(e, e), __NV_SATFINITE, __NV_E4M3) & 0xFF;
+            if (ca != ce) bad8++;
+            const bool both_nan = (a != a) && (e != e);
+            if (!both_nan && fabsf(e) >= 0.000244140625f && __float_as_uint(a) != __float_as_uint(e)) bad32++;
         }
+        if (bad8) atomicAdd(mismatches, static_cast<unsigned long long>(bad8));
+        if (bad32) atomicAdd(mismatches + 1, static_cast<unsigned long long>(bad32));
     }
 }
 
 static int grid_for(size_t warps_needed, int sm_count) {
     size_t blocks = (warps_needed * 32 + kThreads - 1) / kThreads;
-    const size_t cap = static_cast<size_t>(sm_count) * 4;
+    const size_t cap = static_cast<size_t>(sm_count) * 8;    // 2048 threads per SM: latency-bound streams need the occupancy
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     return static_cast<int>(blocks);
@@ -457,6 +549,12 @@ const uint16_t* rdb_ar_result(void* ctx) {
     rdb::ar::Ctx* c = static_cast<rdb::ar::Ctx*>(ctx);
     if (!c) return nullptr;
     return reinterpret_cast<const uint16_t*>(c->ws[c->rank] + c->L.off_gather);
+}
+
+int rdb_debug_division_mismatches(const float* divisors, int count, unsigned long long* mismatches, void* stream) {
+    if (count < 1) return RDB_BAD_SHAPE;
+    rdb::ar::div_check_kernel<<<count < 2048 ? count : 2048, 256, 0, static_cast<cudaStream_t>(stream)>>>(divisors, count, mismatches);
+    return cudaGetLastError() == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
 }
 
 int rdb_quantize_blocks128(const uint16_t* x, uint8_t* q, float* scales, size_t n, void* stream) {

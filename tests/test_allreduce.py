@@ -89,6 +89,44 @@ def test_encoder_is_bit_exact(cuda_device, oracle, n):
 
 
 @pytest.mark.gpu
+def test_encoder_bit_exact_on_many_blocks_and_magnitudes(cuda_device, oracle):
+    """A million blocks whose magnitudes span 2^-120 .. 2^120: scales and codes
+    equal the oracle's (which divides with IEEE divisions)."""
+    import rocm_dev_b200 as R
+    nb = 1 << 14
+    g = torch.Generator().manual_seed(42)
+    mag = torch.exp2(torch.randint(-120, 121, (nb, 1), generator=g).float())
+    x = (torch.randn(nb, 128, generator=g) * mag).bfloat16().reshape(-1)
+    q, s = R.quantize_blocks128(x.to(cuda_device))
+    wq, ws = oracle.quantize_blocks128(_bits(x))
+    assert np.array_equal(s.cpu().numpy().view(np.uint32), ws.view(np.uint32))
+    assert np.array_equal(q.cpu().numpy(), wq)
+
+
+@pytest.mark.gpu
+def test_encoder_division_is_the_ieee_quotient(cuda_device):
+    """The encoder divides by multiplying with a rounded reciprocal and one
+    residual correction; for every bf16 x and a wide set of divisors (random,
+    powers of two, all-ones and near-all-ones significands, tiny, huge, inf,
+    the amax/448 values of real blocks) the e4m3 encoding - and every normal fp32 quotient - equals that of x / s,
+    over all x a block with that scale can contain."""
+    import rocm_dev_b200 as R
+    g = torch.Generator().manual_seed(0)
+    rnd = (torch.randn(20000, generator=g).abs() + 1e-3) * torch.exp2(torch.randint(-40, 40, (20000,), generator=g).float())
+    real = torch.randn(4096, 128, generator=g).bfloat16().float().abs().amax(1) / 448.0
+    special_bits = [0x3F800000, 0x3FFFFFFF, 0x3FFFFFFE, 0x3F800001, 0x00800000, 0x7F7FFFFF, 0x7F800000, 0x0D000000,
+                    0x0E000001, 0x71000000, 0x717FFFFF, 0x3B124925, 0x3C000000, 0x3EAAAAAB, 0x40490FDB]
+    special = torch.tensor(special_bits, dtype=torch.int32).view(torch.float32)
+    ones = (torch.arange(60, 200, dtype=torch.int32) << 23 | 0x7FFFFF).view(torch.float32)
+    s = torch.cat([rnd, real, special, ones, ones.view(torch.int32).sub(1).view(torch.float32)]).to(cuda_device)
+    bad = torch.zeros(2, dtype=torch.int64, device=cuda_device)
+    assert R.lib().rdb_debug_division_mismatches(s.data_ptr(), s.numel(), bad.data_ptr(), 0) == 0
+    torch.cuda.synchronize()
+    assert bad[0].item() == 0, f"{bad[0].item()} encodings differ from those of the IEEE quotient"
+    assert bad[1].item() == 0, f"{bad[1].item()} normal fp32 quotients differ from IEEE division"
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("world", [1, 2, 3, 4, 8])
 @pytest.mark.parametrize("algo", [1, 2])
 def test_emulated_ranks_on_one_gpu(cuda_device, oracle, world, algo):
