@@ -370,8 +370,8 @@ def bench_allreduce(torch, dist, R, dev, rank, world):
     """FP8-encoded allreduce against NCCL's bf16 allreduce on [T, 8192] bf16
     tensors.  busBW = S/t * 2(n-1)/n with S the bf16 size; device time, max over
     ranks.  Reported beside the headline metric when more than one GPU runs."""
-    ar = R.Fp8AllReduce(max_elems=4096 * 8192)
-    out = {"unit": "GB/s busBW", "world": world, "cases": {}}
+    ar = R.Fp8AllReduce(max_elems=4096 * 8192, backend="auto")
+    out = {"unit": "GB/s busBW", "world": world, "workspace": ar.backend, "multimem_all_gather": ar.multicast, "cases": {}}
 
     def timed(fn, iters):
         for _ in range(3):
@@ -396,8 +396,11 @@ def bench_allreduce(torch, dist, R, dev, rank, world):
         iters = 200 if T <= 128 else 40
         t_fp8 = timed(lambda: ar.all_reduce(x, out=y), iters)
         t_nccl = timed(lambda: dist.all_reduce(z), iters)
+        t_ws = timed(lambda: ar.all_reduce_in_workspace(x), iters)     # two-shot, result left in the workspace
         S, f = n * 2, 2 * (world - 1) / world
         out["cases"][f"T{T}"] = {"bytes": S, "fp8_us": round(t_fp8 * 1e6, 2), "nccl_bf16_us": round(t_nccl * 1e6, 2),
+                                 "fp8_in_workspace_us": round(t_ws * 1e6, 2),
+                                 "fp8_in_workspace_busbw": round(S / t_ws * f / 1e9, 1),
                                  "fp8_busbw": round(S / t_fp8 * f / 1e9, 1), "nccl_bf16_busbw": round(S / t_nccl * f / 1e9, 1),
                                  "ratio": round(t_nccl / t_fp8, 3)}
     if R.lib().rdb_device_status() != 0:

@@ -197,6 +197,12 @@ int rdb_ar_ipc_import(const uint8_t *handle64, void **ptr);
 int rdb_ar_ipc_close(void *ptr);
 int rdb_ar_create(int rank, int world, void *const *workspaces, size_t max_elems, void **ctx);
 int rdb_ar_destroy(void *ctx);
+/* Optional: a multicast (NVLS) address that aliases EVERY rank's workspace with
+ * the same layout - e.g. the multicast pointer of a symmetric-memory
+ * allocation used as the workspace.  The bf16 all-gather of the two-shot
+ * algorithm then uses multimem.st (one store reaches all ranks).  NULL switches
+ * back to per-peer stores.  Every rank must make the same choice. */
+int rdb_ar_set_multicast(void *ctx, void *multicast_workspace);
 
 /* Collective: every rank calls it with the same n (a multiple of 128, at most
  * max_elems) and algo (0 automatic, 1 one-shot: every rank receives and

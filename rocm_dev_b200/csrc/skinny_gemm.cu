@@ -127,6 +127,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const uint32_t xbar = smem_u32(bars + 2 * MAX_STAGES + 1);   // split-K partials have arrived
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile float* sc_s = reinterpret_cast<volatile float*>(tmem_slot + 2);   // scale_a * scale_b, fetched early
     const uint32_t stage0 = smem_u32(smem);
 
     if (threadIdx.x == 0) {
@@ -205,6 +206,14 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             tc_commit(tmem_full);            // accumulator complete (also fires after an abort)
         }
         __syncwarp();
+    } else if (warp == 2) {
+        // An otherwise idle warp fetches the two scales while the weights stream,
+        // so that their global-load latency is off the epilogue's critical path.
+        if (lane == 0) {
+            if (p.pdl) pdl_wait_prior();   // the scales may be the preceding kernel's output
+            *sc_s = __ldg(p.scale_a) * __ldg(p.scale_b);
+        }
+        __syncwarp();
     }
 
     const bool vec_ok = (p.N % 4 == 0);
@@ -253,7 +262,7 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     if (S > 1) cluster_wait_acquire();     // phase 1 complete: every peer's barriers and buffers are live
     if (p.pdl) pdl_wait_prior();           // D and the scales may belong to the preceding kernel
     __syncthreads();
-    const float sc = __ldg(p.scale_a) * __ldg(p.scale_b);
+    const float sc = *sc_s;
 
     if (S == 1) {
         // Step 2 - every thread converts and stores 8 consecutive outputs.

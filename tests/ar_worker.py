@@ -15,12 +15,19 @@ sys.path.insert(0, ROOT)
 def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(rank)
-    dist.init_process_group("gloo")          # handles travel over gloo; the data path is the library's own
+    backend = os.environ.get("RDB_AR_BACKEND", "ipc")
+    if backend == "ipc":
+        dist.init_process_group("gloo")      # handles travel over gloo; the data path is the library's own
+    else:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
     import rocm_dev_b200 as R
     from oracle import oracle as O
-    ar = R.Fp8AllReduce(max_elems=4096 * 8192)
+    ar = R.Fp8AllReduce(max_elems=4096 * 8192, backend=backend)
+    print(f"rank {rank} backend {ar.backend} multicast {ar.multicast}")
     dev = torch.device("cuda", rank)
-    cases = [(128, 1), (8192, 1), (8192, 2), (16 * 8192, 0), (128 * 8192, 2), (640, 2), (1024 * 8192, 0)]
+    cases = [(128, 1), (8192, 1), (8192, 2), (16 * 8192, 0), (128 * 8192, 2), (640, 2), (1024 * 8192, 0), (4096 * 8192, 2),
+             (513 * 8192 + 128, 2)]
     for n, algo in cases:
         for rep in range(2):                 # twice: both staging sets, growing epochs
             xs = [torch.randn(n, generator=torch.Generator().manual_seed(1000 * rep + 17 * r + n)).bfloat16()
@@ -32,6 +39,10 @@ def main():
             want, _, _ = O.allreduce_fp8(bits)
             got = out.cpu().view(torch.int16).numpy().view(np.uint16)
             assert np.array_equal(got, want), f"rank {rank} n {n} algo {algo} rep {rep}: {(got != want).sum()} differ"
+            if algo == 2:                    # the same result left in the workspace (no copy-out)
+                view = ar.all_reduce_in_workspace(xs[rank].to(dev))
+                torch.cuda.synchronize()
+                assert np.array_equal(view.cpu().view(torch.int16).numpy().view(np.uint16), want)
     dist.barrier()
     ar.close()
     dist.destroy_process_group()

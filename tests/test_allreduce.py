@@ -190,12 +190,15 @@ def test_error_codes(cuda_device):
 
 
 @pytest.mark.gpu
-def test_two_processes_two_gpus(cuda_device):
-    """Real peer-to-peer path: one process per GPU, workspaces shared by IPC."""
+@pytest.mark.parametrize("backend", ["ipc", "auto"])
+def test_two_processes_two_gpus(cuda_device, backend):
+    """Real peer-to-peer path: one process per GPU; workspaces shared by CUDA
+    IPC, or allocated as symmetric memory (multimem all-gather where the
+    allocation has a multicast address)."""
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(29600 + os.getpid() % 300), WORLD_SIZE="2",
-               NCCL_NVLS_ENABLE="0")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(29600 + os.getpid() % 300 + (7 if backend == "auto" else 0)),
+               WORLD_SIZE="2", RDB_AR_BACKEND=backend)
     procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "ar_worker.py")], env=dict(env, RANK=str(r)),
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
     outs = [p.communicate(timeout=600)[0] for p in procs]
