@@ -126,6 +126,13 @@ int rdb_skinny_gemm_trace(unsigned long long *device_buffer, int slots, int ctas
 int rdb_dense_gemm_fp8(const uint8_t *A, const uint8_t *B, const float *scale_a, const float *scale_b,
                        uint16_t *D, int M, int N, int K, void *stream);
 
+/* Tuner entry of the dense GEMM: tile_rows selects 128 x 256 or 256 x 256 output
+ * tiles (0 = automatic), max_ctas caps the persistent grid (0 = one CTA per
+ * SM).  The reference fixes its tiles with #defines (projects/
+ * async_gemm_16x16x64/core.cu:21-31) and retunes by recompiling (grid.py). */
+int rdb_dense_gemm_fp8_tuned(const uint8_t *A, const uint8_t *B, const float *scale_a, const float *scale_b,
+                             uint16_t *D, int M, int N, int K, int tile_rows, int max_ctas, void *stream);
+
 /* The reference's own output convention for the same projects: unscaled fp32,
  * D [M,N] OVERWRITTEN (async_gemm<float>, same citations). */
 int rdb_dense_gemm_fp8_f32(const uint8_t *A, const uint8_t *B, float *D, int M, int N, int K, void *stream);

@@ -28,6 +28,7 @@ _SIGNATURES = {
     "rdb_skinny_gemm_trace": (i, [vp, i, i]),
     "rdb_skinny_gemm_fp8_tuned": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, i, i, i, C.c_uint, vp]),
     "rdb_dense_gemm_fp8": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, vp]),
+    "rdb_dense_gemm_fp8_tuned": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, i, vp]),
     "rdb_dense_gemm_fp8_f32": (i, [u8p, u8p, vp, i, i, i, vp]),
     "rdb_sparse_gemm_fp8": (i, [u8p, u8p, u8p, f32p, f32p, vp, i, i, i, vp]),
     "rdb_sparse_gemm_fp8_tuned": (i, [u8p, u8p, u8p, f32p, f32p, vp, i, i, i, i, vp]),

@@ -38,7 +38,7 @@ def _stream(dev) -> int:
 
 
 def dense_gemm_fp8(A: torch.Tensor, B: torch.Tensor, scale_a: torch.Tensor, scale_b: torch.Tensor,
-                   out: torch.Tensor | None = None) -> torch.Tensor:
+                   out: torch.Tensor | None = None, tile_rows: int = 0, max_ctas: int = 0) -> torch.Tensor:
     """D[M,N] = bf16((A . B^T) * scale_a * scale_b); A [M,K], B [N,K] e4m3fn bytes."""
     assert A.is_cuda and B.is_cuda and A.is_contiguous() and B.is_contiguous()
     A, B = _u8(A), _u8(B)
@@ -49,8 +49,8 @@ def dense_gemm_fp8(A: torch.Tensor, B: torch.Tensor, scale_a: torch.Tensor, scal
         out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
     assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape == (M, N)
     with torch.cuda.device(A.device):
-        code = lib().rdb_dense_gemm_fp8(A.data_ptr(), B.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(),
-                                        out.data_ptr(), M, N, K, _stream(A.device))
+        code = lib().rdb_dense_gemm_fp8_tuned(A.data_ptr(), B.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(),
+                                              out.data_ptr(), M, N, K, tile_rows, max_ctas, _stream(A.device))
     check(code, "rdb_dense_gemm_fp8")
     return out
 

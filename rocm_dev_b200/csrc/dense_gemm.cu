@@ -26,12 +26,24 @@
 namespace rdb {
 namespace dense {
 
-constexpr int BM = 128, BN = 256, BK = 128;
-constexpr int A_BYTES = BM * BK, B_BYTES = BN * BK, STAGE_BYTES = A_BYTES + B_BYTES;
-constexpr int STAGES = 4;
+constexpr int BN = 256, BK = 128;
+constexpr int RB_BYTES = 128 * BK, B_BYTES = BN * BK;   // one 128-row block of A, the B tile
 constexpr int NUM_THREADS = 192;
 constexpr int GROUP_M = 16;
-constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+
+// RB = 128-row blocks of A per tile.  RB = 1: 128 x 256 tiles, 4 stages, the two
+// TMEM accumulators alternate between consecutive tiles.  RB = 2: 256 x 256
+// tiles - two MMA row blocks share one B tile, which cuts the operand bytes per
+// MMA by a third (64 KiB per 8 MMAs instead of 48 KiB per 4) - 3 stages, and the
+// two accumulators are the two row blocks of the same tile.
+template <int RB>
+struct Cfg {
+    static constexpr int BM = 128 * RB;
+    static constexpr int A_BYTES = RB * RB_BYTES;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGES = RB == 1 ? 4 : 3;
+    static constexpr int SMEM_BYTES = 1024 + STAGES * STAGE_BYTES + 256;
+};
 
 struct Params {
     void* D;
@@ -51,8 +63,11 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
     nb = r / gsize;
 }
 
+template <int RB>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 dense_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, const Params p) {
+    using C = Cfg<RB>;
+    constexpr int STAGES = C::STAGES, STAGE_BYTES = C::STAGE_BYTES, A_BYTES = C::A_BYTES, BM = C::BM;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -109,26 +124,36 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = idesc_e4m3_f32(BM, BN);
+            constexpr uint32_t idesc = idesc_e4m3_f32(128, BN);
             int it = 0, t = 0;
             for (int tile = blockIdx.x; tile < num_tiles && *abort_flag == 0; tile += gridDim.x, t++) {
-                const int acc = t & 1;
-                // the epilogue must have drained this accumulator (two tiles ago)
-                if (!mbar_wait(acc_empty0 + 8 * acc, ((t >> 1) & 1) ^ 1)) { *abort_flag = 1; report_timeout(p.status); break; }
-                tc_fence_after_sync();
-                const uint32_t d = tmem_base + acc * BN;
-                for (int kb = 0; kb < p.num_kb; kb++, it++) {
+                // accumulator buffers: RB = 1 alternates them between tiles, RB = 2 uses one per row block
+                const int acc0 = RB == 1 ? (t & 1) : 0;
+                const uint32_t use = RB == 1 ? (t >> 1) : t;           // how often this buffer has been used before
+                bool ok = true;
+                for (int kb = 0; kb < p.num_kb && ok; kb++, it++) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
-                    if (!mbar_wait(full0 + 8 * s, ph)) { *abort_flag = 1; report_timeout(p.status); break; }
+                    if (!mbar_wait(full0 + 8 * s, ph)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint32_t a = stage0 + s * STAGE_BYTES, b = a + A_BYTES;
 #pragma unroll
-                    for (int ks = 0; ks < BK / 32; ks++)
-                        tc_mma_f8(d, smem_desc_k128(a + ks * 32), smem_desc_k128(b + ks * 32), idesc, (kb | ks) != 0);
+                    for (int rb = 0; rb < RB; rb++) {
+                        const int acc = acc0 + rb;
+                        if (kb == 0) {
+                            // the epilogue must have drained this accumulator
+                            if (!mbar_wait(acc_empty0 + 8 * acc, (use & 1) ^ 1)) { ok = false; break; }
+                            tc_fence_after_sync();
+                        }
+                        const uint32_t d = tmem_base + acc * BN;
+#pragma unroll
+                        for (int ks = 0; ks < BK / 32; ks++)
+                            tc_mma_f8(d, smem_desc_k128(a + rb * RB_BYTES + ks * 32), smem_desc_k128(b + ks * 32), idesc, (kb | ks) != 0);
+                        if (kb == p.num_kb - 1) tc_commit(acc_full0 + 8 * acc);   // this row block is complete
+                    }
                     tc_commit(empty0 + 8 * s);
                 }
-                tc_commit(acc_full0 + 8 * acc);
+                if (!ok) { *abort_flag = 1; report_timeout(p.status); break; }
             }
         }
         __syncwarp();
@@ -139,55 +164,60 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         if (p.scale_a) sc = __ldg(p.scale_a) * __ldg(p.scale_b);
         const bool vec8 = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
         int t = 0;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, t++) {
+        bool live = true;
+        for (int tile = blockIdx.x; tile < num_tiles && live; tile += gridDim.x, t++) {
             int mb, nb;
             tile_coords(tile, p.tiles_m, p.tiles_n, mb, nb);
-            const int acc = t & 1;
-            bool ok = mbar_wait(acc_full0 + 8 * acc, (t >> 1) & 1);
-            if (!ok) { *abort_flag = 1; report_timeout(p.status); }
-            if (*abort_flag != 0) break;
-            tc_fence_after_sync();
-            const int row = mb * BM + quad * 32 + lane;
-            const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 32) {
-                float v[32];
-                tmem_ld32(taddr + c0, v);
-                const int col = nb * BN + c0;
-                if (row < p.M && col < p.N) {
-                    if (p.out_f32) {
-                        float* out = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.N + col;
-                        if (p.N % 4 == 0 && col + 31 < p.N) {
+            for (int rb = 0; rb < RB; rb++) {
+                const int acc = RB == 1 ? (t & 1) : rb;
+                const uint32_t use = RB == 1 ? (t >> 1) : t;
+                bool ok = mbar_wait(acc_full0 + 8 * acc, use & 1);
+                if (!ok) { *abort_flag = 1; report_timeout(p.status); }
+                if (*abort_flag != 0) { live = false; break; }
+                tc_fence_after_sync();
+                const int row = mb * BM + rb * 128 + quad * 32 + lane;
+                const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quad * 32) << 16);
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    float v[32];
+                    tmem_ld32(taddr + c0, v);
+                    const int col = nb * BN + c0;
+                    if (row < p.M && col < p.N) {
+                        if (p.out_f32) {
+                            float* out = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.N + col;
+                            if (p.N % 4 == 0 && col + 31 < p.N) {
 #pragma unroll
-                            for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4*>(out + j) = make_float4(v[j] * sc, v[j + 1] * sc, v[j + 2] * sc, v[j + 3] * sc);
-                        } else {
-                            for (int j = 0; j < 32; j++)
-                                if (col + j < p.N) out[j] = v[j] * sc;
-                        }
-                    } else {
-                        __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.N + col;
-                        if (vec8 && col + 31 < p.N) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                __nv_bfloat162 b0 = __floats2bfloat162_rn(v[j] * sc, v[j + 1] * sc), b1 = __floats2bfloat162_rn(v[j + 2] * sc, v[j + 3] * sc);
-                                __nv_bfloat162 b2 = __floats2bfloat162_rn(v[j + 4] * sc, v[j + 5] * sc), b3 = __floats2bfloat162_rn(v[j + 6] * sc, v[j + 7] * sc);
-                                uint4 o;
-                                o.x = *reinterpret_cast<uint32_t*>(&b0); o.y = *reinterpret_cast<uint32_t*>(&b1);
-                                o.z = *reinterpret_cast<uint32_t*>(&b2); o.w = *reinterpret_cast<uint32_t*>(&b3);
-                                *reinterpret_cast<uint4*>(out + j) = o;
+                                for (int j = 0; j < 32; j += 4)
+                                    *reinterpret_cast<float4*>(out + j) = make_float4(v[j] * sc, v[j + 1] * sc, v[j + 2] * sc, v[j + 3] * sc);
+                            } else {
+                                for (int j = 0; j < 32; j++)
+                                    if (col + j < p.N) out[j] = v[j] * sc;
                             }
                         } else {
-                            for (int j = 0; j < 32; j++)
-                                if (col + j < p.N) out[j] = __float2bfloat16_rn(v[j] * sc);
+                            __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(p.D) + static_cast<size_t>(row) * p.N + col;
+                            if (vec8 && col + 31 < p.N) {
+#pragma unroll
+                                for (int j = 0; j < 32; j += 8) {
+                                    __nv_bfloat162 b0 = __floats2bfloat162_rn(v[j] * sc, v[j + 1] * sc), b1 = __floats2bfloat162_rn(v[j + 2] * sc, v[j + 3] * sc);
+                                    __nv_bfloat162 b2 = __floats2bfloat162_rn(v[j + 4] * sc, v[j + 5] * sc), b3 = __floats2bfloat162_rn(v[j + 6] * sc, v[j + 7] * sc);
+                                    uint4 o;
+                                    o.x = *reinterpret_cast<uint32_t*>(&b0); o.y = *reinterpret_cast<uint32_t*>(&b1);
+                                    o.z = *reinterpret_cast<uint32_t*>(&b2); o.w = *reinterpret_cast<uint32_t*>(&b3);
+                                    *reinterpret_cast<uint4*>(out + j) = o;
+                                }
+                            } else {
+                                for (int j = 0; j < 32; j++)
+                                    if (col + j < p.N) out[j] = __float2bfloat16_rn(v[j] * sc);
+                            }
                         }
                     }
                 }
+                // all of this warp's TMEM reads are complete: hand the accumulator back
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(acc_empty0 + 8 * acc);
             }
-            // all of this warp's TMEM reads are complete: hand the accumulator back
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(acc_empty0 + 8 * acc);
         }
     }
 
@@ -199,25 +229,21 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
     if (warp == 1) tmem_dealloc(tmem_base, 512);
 }
 
-static int run(const uint8_t* A, const uint8_t* B, const float* sa, const float* sb, void* D, int out_f32, int M, int N,
-               int K, int max_ctas, cudaStream_t stream) {
-    if (M < 1 || N < 1 || K < 1) return RDB_BAD_SHAPE;
-    if (K % 16 != 0) return RDB_K_NOT_DIVISIBLE_BY_WARPTILE_K;
-    if (!aligned16(A) || !aligned16(B) || (reinterpret_cast<uintptr_t>(D) & 3u)) return RDB_BAD_ALIGNMENT;
-    if ((sa == nullptr) != (sb == nullptr)) return RDB_INVALID_CONFIG;
-    int err = 0;
-    DeviceInfo* info = device_info(&err);
-    if (!info) return err;
+template <int RB>
+static int launch(const uint8_t* A, const uint8_t* B, const float* sa, const float* sb, void* D, int out_f32, int M, int N,
+                  int K, int max_ctas, DeviceInfo* info, cudaStream_t stream) {
+    using C = Cfg<RB>;
     static bool attr_set[kMaxDevices] = {};
     int dev = 0;
     cudaGetDevice(&dev);
+    auto kernel = dense_gemm_kernel<RB>;
     if (!attr_set[dev]) {
-        if (cudaFuncSetAttribute(dense_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES) != cudaSuccess)
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES) != cudaSuccess)
             return RDB_CUDA_ERROR;
         attr_set[dev] = true;
     }
     CUtensorMap tmA, tmB;
-    int r = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BK, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+    int r = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, BK, C::BM, CU_TENSOR_MAP_SWIZZLE_128B);
     if (r != RDB_SUCCESS) return r;
     r = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, K, BK, BN, CU_TENSOR_MAP_SWIZZLE_128B);
     if (r != RDB_SUCCESS) return r;
@@ -229,15 +255,31 @@ static int run(const uint8_t* A, const uint8_t* B, const float* sa, const float*
     p.M = M;
     p.N = N;
     p.num_kb = (K + BK - 1) / BK;
-    p.tiles_m = (M + BM - 1) / BM;
+    p.tiles_m = (M + C::BM - 1) / C::BM;
     p.tiles_n = (N + BN - 1) / BN;
     p.out_f32 = out_f32;
     int grid = p.tiles_m * p.tiles_n;
     int cap = info->sm_count;
     if (max_ctas > 0 && max_ctas < cap) cap = max_ctas;
     if (grid > cap) grid = cap;
-    dense_gemm_kernel<<<grid, NUM_THREADS, SMEM_BYTES, stream>>>(tmA, tmB, p);
+    kernel<<<grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(tmA, tmB, p);
     return cudaGetLastError() == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
+}
+
+static int run(const uint8_t* A, const uint8_t* B, const float* sa, const float* sb, void* D, int out_f32, int M, int N,
+               int K, int max_ctas, int tile_rows, cudaStream_t stream) {
+    if (M < 1 || N < 1 || K < 1) return RDB_BAD_SHAPE;
+    if (K % 16 != 0) return RDB_K_NOT_DIVISIBLE_BY_WARPTILE_K;
+    if (!aligned16(A) || !aligned16(B) || (reinterpret_cast<uintptr_t>(D) & 3u)) return RDB_BAD_ALIGNMENT;
+    if ((sa == nullptr) != (sb == nullptr)) return RDB_INVALID_CONFIG;
+    int err = 0;
+    DeviceInfo* info = device_info(&err);
+    if (!info) return err;
+    // 256-row tiles unless padding M up to a multiple of 256 would waste more than ~12 % of the work
+    const int m256 = (M + 255) / 256 * 256;
+    const int rb = (tile_rows == 128 || (tile_rows == 0 && (m256 - M) * 8 > M)) ? 1 : 2;
+    return rb == 1 ? launch<1>(A, B, sa, sb, D, out_f32, M, N, K, max_ctas, info, stream)
+                   : launch<2>(A, B, sa, sb, D, out_f32, M, N, K, max_ctas, info, stream);
 }
 
 }  // namespace dense
@@ -248,11 +290,18 @@ extern "C" {
 int rdb_dense_gemm_fp8(const uint8_t* A, const uint8_t* B, const float* scale_a, const float* scale_b, uint16_t* D,
                        int M, int N, int K, void* stream) {
     if (!scale_a || !scale_b) return RDB_INVALID_CONFIG;
-    return rdb::dense::run(A, B, scale_a, scale_b, D, 0, M, N, K, 0, static_cast<cudaStream_t>(stream));
+    return rdb::dense::run(A, B, scale_a, scale_b, D, 0, M, N, K, 0, 0, static_cast<cudaStream_t>(stream));
 }
 
 int rdb_dense_gemm_fp8_f32(const uint8_t* A, const uint8_t* B, float* D, int M, int N, int K, void* stream) {
-    return rdb::dense::run(A, B, nullptr, nullptr, D, 1, M, N, K, 0, static_cast<cudaStream_t>(stream));
+    return rdb::dense::run(A, B, nullptr, nullptr, D, 1, M, N, K, 0, 0, static_cast<cudaStream_t>(stream));
+}
+
+int rdb_dense_gemm_fp8_tuned(const uint8_t* A, const uint8_t* B, const float* scale_a, const float* scale_b, uint16_t* D,
+                             int M, int N, int K, int tile_rows, int max_ctas, void* stream) {
+    if (!scale_a || !scale_b) return RDB_INVALID_CONFIG;
+    if (tile_rows != 0 && tile_rows != 128 && tile_rows != 256) return RDB_INVALID_CONFIG;
+    return rdb::dense::run(A, B, scale_a, scale_b, D, 0, M, N, K, max_ctas, tile_rows, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -40,6 +40,20 @@ def test_ragged_shapes(cuda_device, oracle, M, N, K):
     _check_bf16(oracle, cuda_device, M, N, K, seed=3)
 
 
+@pytest.mark.parametrize("tile_rows", [128, 256])
+@pytest.mark.parametrize("M,N,K", [(512, 512, 1024), (300, 520, 272), (1280, 768, 512)])
+def test_both_tile_heights(cuda_device, oracle, tile_rows, M, N, K):
+    import rocm_dev_b200 as R
+    Aq, Bq, sa, sb = _operands(M, N, K, seed=11)
+    dev = cuda_device
+    out = R.dense_gemm_fp8(Aq.to(dev), Bq.to(dev), sa.to(dev), sb.to(dev), tile_rows=tile_rows, max_ctas=3)
+    torch.cuda.synchronize()
+    assert R.lib().rdb_device_status() == 0
+    ref = oracle.gemm_fp8_bf16(Aq.numpy(), Bq.numpy(), sa.item(), sb.item())
+    ref64, mag = oracle.gemm_fp8_f64(Aq.numpy(), Bq.numpy(), sa.item(), sb.item())
+    check_gemm_parity(bf16_bits(out), ref, ref64, mag, K)
+
+
 def test_many_tiles_per_cta_and_both_accumulators(cuda_device, oracle):
     # 40 x 12 = 480 tiles on 148 CTAs: every CTA runs 3-4 tiles, alternating accumulators
     _check_bf16(oracle, cuda_device, 5120, 3072, 256, seed=5)
