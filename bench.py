@@ -191,6 +191,8 @@ def run_gpu(args):
 
     flags = R.OVERLAP_PRIOR_KERNEL   # weights are never written inside the timed region
 
+    if args.single and not args.single.split("_M")[0] in [n for n, _, _ in SHAPES]:
+        return run_single_other(args, torch, R, quant, dev)
     if args.single:
         # profiling aid: plain launches of one (shape, M) case, weight copies rotating
         name, m = args.single.rsplit("_M", 1)
@@ -407,6 +409,53 @@ def bench_allreduce(torch, dist, R, dev, rank, world):
         out["error"] = "device status word reports a timed-out wait"
     ar.close()
     return out
+
+
+def run_single_other(args, torch, R, quant, dev):
+    """Profiling aid for the other kernels: plain launches of one small case.
+    dense_<n> (n^3), sparse_M<m> (N=K=8192), reduce_<b>x<m>x<n>, quantize_T<t> ([t,8192] bf16)."""
+    one = torch.ones(1, device=dev)
+    kind, _, arg = args.single.partition("_")
+    reps = args.warmup + args.steps
+    if kind == "dense":
+        n = int(arg)
+        A = torch.randint(0, 0x78, (n, n), dtype=torch.uint8, device=dev)
+        B = torch.randint(0, 0x78, (n, n), dtype=torch.uint8, device=dev)
+        D = torch.empty((n, n), dtype=torch.bfloat16, device=dev)
+        for _ in range(reps):
+            R.dense_gemm_fp8(A, B, one, one, out=D)
+        work = {"flops_per_launch": 2.0 * n ** 3}
+    elif kind == "sparse":
+        M, N, K = int(arg[1:]), 8192, 8192
+        packs = []
+        for c in range(2):
+            W = (torch.randn((N, K), generator=torch.Generator().manual_seed(c)) * 0.02).bfloat16()
+            Wq, _ = quant.quantize_per_tensor(R.prune_2of4(W))
+            v, m = R.pack_2of4(Wq)
+            packs.append((v.to(dev), m.to(dev)))
+        A = torch.randint(0, 0x78, (M, K), dtype=torch.uint8, device=dev)
+        D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+        for i in range(reps):
+            R.sparse_gemm_fp8(A, packs[i % 2][0], packs[i % 2][1], one, one, out=D)
+        work = {"algorithmic_bytes_per_launch": N * K // 2 + N * K // 8 + M * K + 2 * M * N}
+    elif kind == "reduce":
+        b, m, n = (int(x) for x in arg.split("x"))
+        A = torch.rand((b, m, n), device=dev)
+        B = torch.rand((b, m, n), device=dev)
+        D = torch.empty((m, n), device=dev)
+        for _ in range(reps):
+            R.tiled_sum_reduce(A, B, D, b, m, n)
+        work = {"algorithmic_bytes_per_launch": 8 * b * m * n + 4 * m * n}
+    elif kind == "quantize":
+        n = int(arg[1:]) * 8192
+        x = torch.randn(n, device=dev).bfloat16()
+        for _ in range(reps):
+            R.quantize_blocks128(x)
+        work = {"algorithmic_bytes_per_launch": n * 2 + n + n // 32}
+    else:
+        raise SystemExit(f"unknown --single case {args.single}")
+    torch.cuda.synchronize()
+    print(json.dumps({"single": args.single, "launches": reps, **work}))
 
 
 # ------------------------------------------------------- secondary suites
