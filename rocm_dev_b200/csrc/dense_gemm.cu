@@ -275,9 +275,12 @@ static int run(const uint8_t* A, const uint8_t* B, const float* sa, const float*
     int err = 0;
     DeviceInfo* info = device_info(&err);
     if (!info) return err;
-    // 256-row tiles unless padding M up to a multiple of 256 would waste more than ~12 % of the work
+    // 256-row tiles when they still fill the machine (at least one tile per SM) and padding M up to
+    // a multiple of 256 wastes no more than ~12 % of the work; else 128-row tiles
     const int m256 = (M + 255) / 256 * 256;
-    const int rb = (tile_rows == 128 || (tile_rows == 0 && (m256 - M) * 8 > M)) ? 1 : 2;
+    const long long tiles256 = static_cast<long long>(m256 / 256) * ((N + BN - 1) / BN);
+    const bool want256 = tiles256 >= info->sm_count && (m256 - M) * 8 <= M;
+    const int rb = (tile_rows == 128 || (tile_rows == 0 && !want256)) ? 1 : 2;
     return rb == 1 ? launch<1>(A, B, sa, sb, D, out_f32, M, N, K, max_ctas, info, stream)
                    : launch<2>(A, B, sa, sb, D, out_f32, M, N, K, max_ctas, info, stream);
 }

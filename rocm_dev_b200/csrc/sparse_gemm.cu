@@ -56,7 +56,7 @@ struct Params {
     int* status;
     int M, N;
     int num_kb;                // K / 256
-    int NB;                    // padded batch (UMMA N)
+    int NB;                    // padded batch columns per CTA (UMMA N); blockIdx.z selects the batch block
     int nstages;
     int ring_bytes;
 };
@@ -98,6 +98,8 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = gridDim.x, rank = blockIdx.x;      // cluster = K slices of one tile
     const int tile = blockIdx.y, n0 = tile * BM;
+    const int m0 = blockIdx.z * p.NB;                 // first batch row of this CTA
+    const int m_count = p.M - m0 < p.NB ? p.M - m0 : p.NB;
     const int NB = p.NB, nstages = p.nstages;
     const int STAGE = stage_bytes(NB);
     const int kb_begin = static_cast<int>((static_cast<long long>(p.num_kb) * rank) / S);
@@ -138,7 +140,8 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 
     if (warp == 0) {
         if (lane == 0) {
-            const uint64_t pol_w = l2_policy_evict_first(), pol_x = l2_policy_evict_last();
+            // with several batch blocks the weights are read once per block: keep them in L2 for the sibling
+            const uint64_t pol_w = gridDim.z > 1 ? l2_policy_evict_last() : l2_policy_evict_first(), pol_x = l2_policy_evict_last();
             const uint8_t* meta_tile = p.meta + static_cast<size_t>(tile) * (2 * p.num_kb) * ATOM_BYTES;
             for (int i = 0; i < nkb; i++) {
                 const int s = i % nstages;
@@ -148,8 +151,8 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                 const uint32_t dst = stage0 + s * STAGE, bar = full0 + 8 * s;
                 mbar_arrive_expect_tx(bar, STAGE);
                 tma_load_2d(dst, &tmW, kb * BKC, n0, bar, pol_w);
-                tma_load_2d(dst + A_BYTES, &tmX, kb * 256, 0, bar, pol_x);
-                tma_load_2d(dst + A_BYTES + NB * 128, &tmX, kb * 256 + 128, 0, bar, pol_x);
+                tma_load_2d(dst + A_BYTES, &tmX, kb * 256, m0, bar, pol_x);
+                tma_load_2d(dst + A_BYTES + NB * 128, &tmX, kb * 256 + 128, m0, bar, pol_x);
                 bulk_load(dst + A_BYTES + 2 * NB * 128, meta_tile + static_cast<size_t>(2 * kb) * ATOM_BYTES, E_BYTES, bar);
             }
         }
@@ -206,14 +209,14 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     if (S == 1) {
         if (*abort_flag == 0) {
             // item = (batch row m, pair of weight rows): one bf16x2 store, coalesced along n
-            for (int item = threadIdx.x; item < p.M * (BM / 2); item += NUM_THREADS) {
+            for (int item = threadIdx.x; item < m_count * (BM / 2); item += NUM_THREADS) {
                 const int m = item / (BM / 2), r = (item - m * (BM / 2)) * 2;
                 const int n = n0 + r;
                 if (n + 1 < p.N) {
-                    *reinterpret_cast<__nv_bfloat162*>(p.D + static_cast<size_t>(m) * p.N + n) =
+                    *reinterpret_cast<__nv_bfloat162*>(p.D + static_cast<size_t>(m0 + m) * p.N + n) =
                         __floats2bfloat162_rn(stg[r * pitch + m] * sc, stg[(r + 1) * pitch + m] * sc);
                 } else if (n < p.N) {
-                    p.D[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(stg[r * pitch + m] * sc);
+                    p.D[static_cast<size_t>(m0 + m) * p.N + n] = __float2bfloat16_rn(stg[r * pitch + m] * sc);
                 }
             }
         }
@@ -230,7 +233,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (!mbar_wait(xbar, 0)) { *abort_flag = 1; report_timeout(p.status); }
         __syncthreads();
         if (*abort_flag == 0) {
-            for (int item = threadIdx.x; item < p.M * (rows_per / 2); item += NUM_THREADS) {
+            for (int item = threadIdx.x; item < m_count * (rows_per / 2); item += NUM_THREADS) {
                 const int m = item / (rows_per / 2), rl = (item - m * (rows_per / 2)) * 2;
                 float s0 = 0.f, s1 = 0.f;
                 for (int src = 0; src < S; src++) {                 // rank order
@@ -239,9 +242,9 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                 }
                 const int n = n0 + rank * rows_per + rl;
                 if (n + 1 < p.N) {
-                    *reinterpret_cast<__nv_bfloat162*>(p.D + static_cast<size_t>(m) * p.N + n) = __floats2bfloat162_rn(s0 * sc, s1 * sc);
+                    *reinterpret_cast<__nv_bfloat162*>(p.D + static_cast<size_t>(m0 + m) * p.N + n) = __floats2bfloat162_rn(s0 * sc, s1 * sc);
                 } else if (n < p.N) {
-                    p.D[static_cast<size_t>(m) * p.N + n] = __float2bfloat16_rn(s0 * sc);
+                    p.D[static_cast<size_t>(m0 + m) * p.N + n] = __float2bfloat16_rn(s0 * sc);
                 }
             }
         }
@@ -266,7 +269,10 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
     int err = 0;
     DeviceInfo* info = device_info(&err);
     if (!info) return err;
-    const int NB = (M + 15) / 16 * 16;
+    // Wide batches are cut into blocks of at most 128 columns along a third grid
+    // dimension: more CTAs, and each re-reads only its own part of the activations.
+    const int mblocks = M > 128 ? (M + 127) / 128 : 1;
+    const int NB = ((M + mblocks - 1) / mblocks + 15) / 16 * 16;
     const int tiles = (N + BM - 1) / BM;
     const int num_kb = K / 256;
     int S = split_k_hint;
@@ -274,8 +280,8 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
         // resident clusters of 2 / 4 CTAs on a 148-SM part: 74 / 33 (one per SM)
         S = 1;
         if (NB <= 64) {
-            if (tiles * 4 <= info->sm_count && tiles <= 33 * info->sm_count / 148) S = 4;
-            else if (tiles * 2 <= info->sm_count) S = 2;
+            if (tiles * mblocks * 4 <= info->sm_count && tiles * mblocks <= 33 * info->sm_count / 148) S = 4;
+            else if (tiles * mblocks * 2 <= info->sm_count) S = 2;
         }
     }
     while (S > 1 && (S > num_kb || NB > 64)) S /= 2;
@@ -316,7 +322,7 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
     p.ring_bytes = ring;
 
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(S, tiles, 1);
+    cfg.gridDim = dim3(S, tiles, mblocks);
     cfg.blockDim = dim3(NUM_THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem_bytes(NB, S, stages);
     cfg.stream = stream;
