@@ -531,7 +531,8 @@ def run_suite(args):
             except Exception:  # noqa: BLE001
                 pass
             tf = 2.0 * n * n * n / us / 1e6
-            cases[str(n)] = {"us": round(us, 1), "tflops": round(tf, 1), "frac_of_4500_nominal": round(tf / 4500, 3),
+            cases[str(n)] = {"us": round(us, 1), "tflops": round(tf, 1), "tflops_per_gpu": round(tf / world, 1),
+                             "frac_of_4500_nominal_per_gpu": round(tf / world / 4500, 3),
                              "cublaslt_fp8_tflops": round(2.0 * n ** 3 / lib_us / 1e6, 1) if lib_us else None}
             del A, B, D
         out.update({"metric": "dense FP8 GEMM TFLOP/s (whole job)", "unit": "TFLOP/s", "scaling": "strong",

@@ -10,8 +10,9 @@
 //
 // Data path.  Each rank owns a workspace (cudaMalloc'd, exported through CUDA
 // IPC) holding a staging area for incoming encoded blocks, a gather area for
-// the bf16 result and flag words.  A call runs three launches on the caller's
-// stream:
+// the bf16 result and flag words.  A call consists of three phases - run as ONE
+// kernel by rdb_ar_allreduce (ar_fused_kernel), or as three launches by
+// rdb_ar_phase when several ranks are emulated on one GPU:
 //   phase 1  quantise the local vector and PUSH the encoded bytes and scales
 //            straight into the staging slot of the rank that owns each
 //            512-element group (two-shot) or of every rank (one-shot, small
@@ -35,9 +36,10 @@
 // (rdb_ar_set_multicast), phase 2 delivers the bf16 result with multimem.st:
 // one store per 16 bytes, replicated by the switch.
 //
-// The three phases are separate launches rather than one cooperative kernel so
-// that a single GPU can emulate W ranks legally (all phase-1 launches, then all
-// phase-2 launches, ...): no launch then waits on one that has not been issued.
+// The phases also exist as separate launches so that a single GPU can emulate W
+// ranks legally (all phase-1 launches, then all phase-2 launches, ...): no
+// launch then waits on one that has not been issued.  The fused kernel must
+// never be used that way.
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
@@ -282,7 +284,7 @@ __device__ __forceinline__ void load_group(const __nv_bfloat16* x, size_t n, siz
     }
 }
 
-__global__ void __launch_bounds__(kThreads) ar_push_kernel(const KParams p) {
+__device__ __forceinline__ void push_body(const KParams& p) {
     const int lane = threadIdx.x & 31;
     const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
     const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
@@ -317,12 +319,15 @@ __global__ void __launch_bounds__(kThreads) ar_push_kernel(const KParams p) {
             }
         }
     }
+}
+
+__global__ void __launch_bounds__(kThreads) ar_push_kernel(const KParams p) {
+    push_body(p);
     publish_when_grid_done(p, 0);
 }
 
 // ------------------------------------------------------------------ phase 2
-__global__ void __launch_bounds__(kThreads) ar_reduce_kernel(const KParams p) {
-    const bool arrived = wait_flags(p, 0);
+__device__ __forceinline__ void reduce_body(const KParams& p, bool arrived) {
     const int lane = threadIdx.x & 31;
     const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
     const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
@@ -371,12 +376,15 @@ __global__ void __launch_bounds__(kThreads) ar_reduce_kernel(const KParams p) {
             }
         }
     }
+}
+
+__global__ void __launch_bounds__(kThreads) ar_reduce_kernel(const KParams p) {
+    reduce_body(p, wait_flags(p, 0));
     if (!p.one_shot) publish_when_grid_done(p, 1);   // also after a timeout, so that peers are not left waiting
 }
 
 // ------------------------------------------------------------------ phase 3
-__global__ void __launch_bounds__(kThreads) ar_gather_kernel(const KParams p) {
-    if (!wait_flags(p, 1)) return;
+__device__ __forceinline__ void copy_out_body(const KParams& p) {
     if (p.out == nullptr) return;
     const uint4* src = reinterpret_cast<const uint4*>(p.ws[p.rank] + p.L.off_gather);
     uint4* dst = reinterpret_cast<uint4*>(p.out);
@@ -384,6 +392,27 @@ __global__ void __launch_bounds__(kThreads) ar_gather_kernel(const KParams p) {
     for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n16;
          i += static_cast<size_t>(gridDim.x) * blockDim.x)
         dst[i] = __ldcg(src + i);
+}
+
+__global__ void __launch_bounds__(kThreads) ar_gather_kernel(const KParams p) {
+    if (!wait_flags(p, 1)) return;
+    copy_out_body(p);
+}
+
+// The whole call in ONE launch: every CTA pushes its share, the last one to
+// finish publishes this rank's flag, every CTA then waits for all ranks' flags
+// (its own included, which covers the pushes of its sibling CTAs), reduces, and
+// - two-shot - repeats the publish / wait step before copying the result out.
+// All CTAs must be resident together (the grid is capped accordingly), because
+// early CTAs wait for the last one.  Not usable when several ranks share one
+// GPU: that case uses the three separate launches above.
+__global__ void __launch_bounds__(kThreads) ar_fused_kernel(const KParams p) {
+    push_body(p);
+    publish_when_grid_done(p, 0);
+    reduce_body(p, wait_flags(p, 0));
+    if (p.one_shot) return;
+    publish_when_grid_done(p, 1);
+    if (wait_flags(p, 1)) copy_out_body(p);
 }
 
 // Standalone encoder (the quantise step alone, for bit-exact tests and callers
@@ -465,7 +494,9 @@ static int run_phase(Ctx* c, int phase, const uint16_t* x, uint16_t* out, size_t
     p.x = reinterpret_cast<const __nv_bfloat16*>(x);
     p.out = reinterpret_cast<__nv_bfloat16*>(out);
     p.status = info->status_dev;
-    if (phase == 1) {
+    if (phase == 0) {
+        ar_fused_kernel<<<grid_for(p.groups, info->sm_count), kThreads, 0, stream>>>(p);
+    } else if (phase == 1) {
         ar_push_kernel<<<grid_for(p.groups, info->sm_count), kThreads, 0, stream>>>(p);
     } else if (phase == 2) {
         const size_t mine = p.one_shot ? p.groups : (p.groups + c->world - 1) / c->world;
@@ -560,11 +591,7 @@ int rdb_ar_allreduce(void* ctx, const uint16_t* x, uint16_t* out, size_t n, int 
     // chunk i+1 over the all-gather of chunk i) was measured slower than one
     // call (187 vs 157 us at 64 MiB on two GPUs): not done.
     const unsigned epoch = ++c->epoch;
-    for (int phase = 1; phase <= 3; phase++) {
-        r = run_phase(c, phase, x, out, n, algo, epoch, static_cast<cudaStream_t>(stream));
-        if (r != RDB_SUCCESS) return r;
-    }
-    return RDB_SUCCESS;
+    return run_phase(c, 0, x, out, n, algo, epoch, static_cast<cudaStream_t>(stream));   // 0 = all phases in one launch
 }
 
 int rdb_ar_begin_call(void* ctx) {
