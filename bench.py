@@ -413,7 +413,7 @@ def bench_allreduce(torch, dist, R, dev, rank, world):
 
 def run_single_other(args, torch, R, quant, dev):
     """Profiling aid for the other kernels: plain launches of one small case.
-    dense_<n> (n^3), sparse_M<m> (N=K=8192), reduce_<b>x<m>x<n>, quantize_T<t> ([t,8192] bf16)."""
+    dense_<n> (n^3), sparse_M<m> (N=K=8192), reduce_<b>x<m>x<n>, quantize_T<t> ([t,8192] bf16, per-128 blocks), quantizept_T<t> (per tensor)."""
     one = torch.ones(1, device=dev)
     kind, _, arg = args.single.partition("_")
     reps = args.warmup + args.steps
@@ -452,6 +452,20 @@ def run_single_other(args, torch, R, quant, dev):
         for _ in range(reps):
             R.quantize_blocks128(x)
         work = {"algorithmic_bytes_per_launch": n * 2 + n + n // 32}
+    elif kind == "quantizept":
+        n = int(arg[1:]) * 8192
+        x = [torch.randn(n, device=dev).bfloat16() for _ in range(2)]
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        for i in range(reps):
+            if i == args.warmup:
+                ev[0].record()
+            quant.quantize_per_tensor_device(x[i % 2])
+        ev[1].record()
+        torch.cuda.synchronize()
+        us = ev[0].elapsed_time(ev[1]) * 1e3 / max(1, args.steps)
+        # the tensor is read twice (maximum, then conversion); the second read may hit L2
+        work = {"algorithmic_bytes_per_launch": n * 2 * 2 + n, "us_per_launch": round(us, 2),
+                "gbs": round((n * 5) / us * 1e-3, 1)}
     else:
         raise SystemExit(f"unknown --single case {args.single}")
     torch.cuda.synchronize()

@@ -232,6 +232,13 @@ int rdb_ar_phase(void *ctx, int phase, int epoch, const uint16_t *x, uint16_t *o
  * vector (n a multiple of 128), bit-exact with the definition above. */
 int rdb_quantize_blocks128(const uint16_t *x, uint8_t *q, float *scales, size_t n, void *stream);
 
+/* Per-tensor quantiser, the step before every GEMM above: scale[0] = amax/448
+ * (1 for an all-zero tensor), q[i] = e4m3fn_sat_rn(x[i] / scale[0]) for a bf16
+ * vector x of n elements (device pointers; x 16-byte aligned).  One kernel;
+ * bit-exact with the host rule.  The reference's drivers draw fp8 values
+ * directly (projects/common.cuh:97-105) and have no counterpart. */
+int rdb_quantize_per_tensor(const uint16_t *x, uint8_t *q, float *scale, size_t n, void *stream);
+
 /* Diagnostic for the encoder's division: for each of `count` fp32 divisors
  * (device array) and every bf16 bit pattern x a block with that scale can hold
  * (|x| <= 512 * divisor, NaN included) compares the encoder's quotient with

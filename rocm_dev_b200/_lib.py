@@ -51,6 +51,7 @@ _SIGNATURES = {
     "rdb_ar_begin_call": (i, [vp]),
     "rdb_ar_phase": (i, [vp, i, i, vp, vp, C.c_size_t, i, vp]),
     "rdb_debug_division_mismatches": (i, [vp, i, vp, vp]),
+    "rdb_quantize_per_tensor": (i, [vp, vp, vp, C.c_size_t, vp]),
     "rdb_quantize_blocks128": (i, [vp, vp, vp, C.c_size_t, vp]),
     "rdb_globs_n_noalloc": (i, [vp, i, i, i, vp]),
     "rdb_noalloc_status": (i, []),

@@ -44,8 +44,10 @@
 #include <cuda_fp8.h>
 #include <cuda_runtime.h>
 
+#include <cstdlib>
 #include <cstring>
 
+#include "fp8_codec.cuh"
 #include "host_util.h"
 #include "ptx.cuh"
 
@@ -89,6 +91,7 @@ struct Ctx {
     uint8_t* ws[kMaxWorld];
     uint8_t* mc;          // optional NVLS multicast alias of the workspace (same layout), else nullptr
     unsigned epoch;
+    int push_order;       // 0 linear, 1 rotated by rank, 2 owner-interleaved (default)
 };
 
 struct KParams {
@@ -100,6 +103,7 @@ struct KParams {
     size_t groups;       // ceil(n / 512)
     unsigned epoch;
     int one_shot;
+    int push_order;
     const __nv_bfloat16* x;
     __nv_bfloat16* out;  // may be nullptr (two-shot: result stays in the gather area)
     int* status;
@@ -122,56 +126,6 @@ __device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
     unsigned v;
     asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
-}
-
-// x / s rounded to nearest, for a divisor shared by a whole block.  With inv =
-// RN(1/s), q0 = RN(x*inv), r = x - q0*s (exact, one FMA) and q = RN(q0 + r*inv)
-// the result equals the IEEE quotient (Markstein's correction step) whenever
-// the quotient neither overflows nor goes subnormal - and inside a block
-// |x| <= amax = 448 s, so |x/s| <= 448, while quotients below 2^-10 encode to
-// zero either way.  Three FMA-class instructions replace a full division,
-// which had made the encoder compute-bound.  `fast` is decided once per block:
-// divisors that are non-finite, tiny, huge or have an all-ones significand take
-// the IEEE division.  NaN elements stay NaN on both paths.
-struct BlockDivisor {
-    float s, inv;
-    bool fast;
-    __device__ __forceinline__ void set(float scale) {
-        s = scale;
-        const uint32_t u = __float_as_uint(scale);
-        const uint32_t e = (u >> 23) & 0xFF;
-        // 2^-80 <= s < 2^100: for every quotient that can reach the e4m3 grid (|q| >= 2^-12)
-        // the residual x - q0*s is then a normal number, hence exact
-        fast = (e > 46) && (e < 227) && ((u & 0x7FFFFFu) != 0x7FFFFFu);
-        inv = __frcp_rn(scale);
-    }
-    __device__ __forceinline__ float div_fast(float x) const {
-        const float q0 = __fmul_rn(x, inv);
-        const float r = __fmaf_rn(-q0, s, x);
-        return copysignf(__fmaf_rn(r, inv, q0), x);      // s > 0; keeps the sign of a zero quotient
-    }
-    // 8 quotients of one lane
-    __device__ __forceinline__ void div8(const float* x, float* q) const {
-        if (fast) {
-#pragma unroll
-            for (int i = 0; i < 8; i++) q[i] = div_fast(x[i]);
-        } else {
-#pragma unroll 1
-            for (int i = 0; i < 8; i++) q[i] = __fdiv_rn(x[i], s);
-        }
-    }
-};
-
-// amax / 448 rounded to nearest: the same correction step with the constant
-// divisor 448 (its reciprocal is rounded at compile time); amax below 2^-100
-// takes the IEEE division.
-__device__ __forceinline__ float block_scale(float amax) {
-    if (!(amax > 0.0f)) return 1.0f;
-    if (amax < 7.888609e-31f || !(amax < 3.0e38f)) return __fdiv_rn(amax, 448.0f);
-    constexpr float inv448 = 1.0f / 448.0f;
-    const float q0 = __fmul_rn(amax, inv448);
-    const float r = __fmaf_rn(-q0, 448.0f, amax);
-    return __fmaf_rn(r, inv448, q0);
 }
 
 // Encodes 8 consecutive bf16 elements (one uint4) held by this lane; the 16
@@ -288,7 +242,39 @@ __device__ __forceinline__ void push_body(const KParams& p) {
     const int lane = threadIdx.x & 31;
     const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
     const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
-    for (size_t g = warp; g < p.groups; g += nwarps) {
+    // Two-shot: group g belongs to one owner rank.  Walking the groups in linear
+    // order would make every rank push to owner 0 at the same time, then to owner
+    // 1, ...: one receiver's link carries all the traffic while the others idle.
+    // Order 2 deals consecutive work items to consecutive owners starting after
+    // this rank, so that each sender's traffic is spread evenly over all
+    // receivers at every moment; order 1 walks linearly from the next rank's shard.
+    const size_t shard_max = (p.groups + p.world - 1) / p.world;
+    const size_t items = (p.one_shot || p.push_order != 2) ? p.groups : shard_max * p.world;
+    const size_t rot = (!p.one_shot && p.push_order == 1) ? group_begin((p.rank + 1) % p.world, p.groups, p.world) : 0;
+    for (size_t it = warp; it < items; it += nwarps) {
+        size_t g, slot_g;
+        int first, last;
+        if (p.one_shot) {
+            g = slot_g = it;
+            first = 0;
+            last = p.world - 1;
+        } else if (p.push_order == 2) {
+            int o = static_cast<int>(it % p.world) + p.rank + 1;
+            while (o >= p.world) o -= p.world;
+            slot_g = it / p.world;
+            const size_t b = group_begin(o, p.groups, p.world);
+            if (b + slot_g >= group_begin(o + 1, p.groups, p.world)) continue;   // this owner's shard is one group shorter
+            g = b + slot_g;
+            first = last = o;
+        } else {
+            g = it + rot;
+            if (g >= p.groups) g -= p.groups;
+            int o = static_cast<int>((g * p.world + p.world - 1) / p.groups);   // owner: largest o with begin(o) <= g
+            while (o + 1 < p.world && group_begin(o + 1, p.groups, p.world) <= g) o++;
+            while (o > 0 && group_begin(o, p.groups, p.world) > g) o--;
+            first = last = o;
+            slot_g = g - group_begin(o, p.groups, p.world);
+        }
         uint4 in[2];
         load_group(p.x, p.n, g, lane, in);
         uint2 q[2];
@@ -297,16 +283,6 @@ __device__ __forceinline__ void push_body(const KParams& p) {
         for (int h = 0; h < 2; h++) q[h] = encode8(in[h], s[h]);
         // the four block scales of the group: (half 0: lanes 0, 16), (half 1: lanes 0, 16)
         const float s1 = __shfl_sync(0xffffffffu, s[0], 16), s3 = __shfl_sync(0xffffffffu, s[1], 16);
-        int first, last;
-        size_t slot_g;
-        if (p.one_shot) { first = 0; last = p.world - 1; slot_g = g; }
-        else {
-            int o = static_cast<int>((g * p.world + p.world - 1) / p.groups);   // owner: largest o with begin(o) <= g
-            while (o + 1 < p.world && group_begin(o + 1, p.groups, p.world) <= g) o++;
-            while (o > 0 && group_begin(o, p.groups, p.world) > g) o--;
-            first = last = o;
-            slot_g = g - group_begin(o, p.groups, p.world);
-        }
         const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + p.rank) * p.L.slot_groups + slot_g;
         for (int peer = first; peer <= last; peer++) {
             uint8_t* base = p.ws[peer];
@@ -371,8 +347,11 @@ __device__ __forceinline__ void reduce_body(const KParams& p, bool arrived) {
             } else if (p.mc) {
                 multimem_st_v4(p.mc + p.L.off_gather + e0 * 2, val);
             } else {
-                for (int peer = 0; peer < p.world; peer++)
+                for (int i = 0; i < p.world; i++) {
+                    int peer = p.rank + 1 + i;
+                    if (peer >= p.world) peer -= p.world;
                     *reinterpret_cast<uint4*>(p.ws[peer] + p.L.off_gather + e0 * 2) = val;
+                }
             }
         }
     }
@@ -491,6 +470,7 @@ static int run_phase(Ctx* c, int phase, const uint16_t* x, uint16_t* out, size_t
     p.groups = (n + kGroup - 1) / kGroup;
     p.epoch = epoch;
     p.one_shot = algo == 1 ? 1 : 0;
+    p.push_order = c->push_order;
     p.x = reinterpret_cast<const __nv_bfloat16*>(x);
     p.out = reinterpret_cast<__nv_bfloat16*>(out);
     p.status = info->status_dev;
@@ -565,6 +545,9 @@ int rdb_ar_create(int rank, int world, void* const* workspaces, size_t max_elems
     for (int i = 0; i < rdb::ar::kMaxWorld; i++) c->ws[i] = i < world ? static_cast<uint8_t*>(workspaces[i]) : nullptr;
     c->mc = nullptr;
     c->epoch = 0;
+    // tuning override for A/B measurements: RDB_AR_PUSH_ORDER = 0 (linear), 1 (rotated), 2 (interleaved, default)
+    const char* po = getenv("RDB_AR_PUSH_ORDER");
+    c->push_order = (po && po[0] >= '0' && po[0] <= '2' && !po[1]) ? po[0] - '0' : 2;
     *ctx = c;
     return RDB_SUCCESS;
 }

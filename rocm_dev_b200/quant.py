@@ -56,3 +56,16 @@ def synthetic_weights_fast(N: int, K: int, seed: int, device="cpu"):
     amax = w.abs().max()
     return (w * (E4M3_MAX / amax)).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).view(torch.uint8), \
         (amax / E4M3_MAX * 0.02).reshape(1)
+
+
+def quantize_per_tensor_device(x: torch.Tensor):
+    """The same rule on the GPU (rdb_quantize_per_tensor): x bf16 CUDA tensor ->
+    (q uint8 like x, scale fp32[1]), bit-exact with ``quantize_per_tensor``."""
+    from ._lib import check, lib
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
+    q = torch.empty(x.shape, dtype=torch.uint8, device=x.device)
+    s = torch.empty(1, dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        check(lib().rdb_quantize_per_tensor(x.data_ptr(), q.data_ptr(), s.data_ptr(), x.numel(),
+                                            torch.cuda.current_stream(x.device).cuda_stream), "rdb_quantize_per_tensor")
+    return q, s
