@@ -58,6 +58,7 @@ constexpr int kMaxWorld = 8;
 constexpr int kGroup = 512;               // elements per work item: 4 blocks of 128
 constexpr size_t kOneShotMaxElems = 1u << 20;
 constexpr int kThreads = 256;
+constexpr int kBlocksPerSm = 4;     // resident blocks per SM the grids are sized for
 
 struct Layout {
     size_t slot_groups;   // groups one source rank may push into one slot
@@ -385,7 +386,7 @@ __global__ void __launch_bounds__(kThreads) ar_gather_kernel(const KParams p) {
 // All CTAs must be resident together (the grid is capped accordingly), because
 // early CTAs wait for the last one.  Not usable when several ranks share one
 // GPU: that case uses the three separate launches above.
-__global__ void __launch_bounds__(kThreads) ar_fused_kernel(const KParams p) {
+__global__ void __launch_bounds__(kThreads, kBlocksPerSm) ar_fused_kernel(const KParams p) {
     push_body(p);
     publish_when_grid_done(p, 0);
     reduce_body(p, wait_flags(p, 0));
@@ -447,9 +448,22 @@ __global__ void div_check_kernel(const float* __restrict__ s, int ns, unsigned l
 // Four blocks per SM: two calls issued on different streams then still fit on
 // the machine together, so a kernel that waits for a peer cannot keep the
 // launch that peer is waiting for off the GPU.
-static int grid_for(size_t warps_needed, int sm_count) {
+// The fused kernel's blocks wait on one another (through the flags of all
+// ranks), so its whole grid must be resident: the cap is what the occupancy
+// calculator reports for the compiled kernel, not an assumed figure.
+static int fused_blocks_per_sm() {
+    static int cached = 0;
+    if (cached == 0) {
+        int nb = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, ar_fused_kernel, kThreads, 0) != cudaSuccess || nb < 1) nb = 1;
+        cached = nb < kBlocksPerSm ? nb : kBlocksPerSm;
+    }
+    return cached;
+}
+
+static int grid_for(size_t warps_needed, int sm_count, int blocks_per_sm = kBlocksPerSm) {
     size_t blocks = (warps_needed * 32 + kThreads - 1) / kThreads;
-    const size_t cap = static_cast<size_t>(sm_count) * 4;
+    const size_t cap = static_cast<size_t>(sm_count) * blocks_per_sm;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     return static_cast<int>(blocks);
@@ -475,7 +489,7 @@ static int run_phase(Ctx* c, int phase, const uint16_t* x, uint16_t* out, size_t
     p.out = reinterpret_cast<__nv_bfloat16*>(out);
     p.status = info->status_dev;
     if (phase == 0) {
-        ar_fused_kernel<<<grid_for(p.groups, info->sm_count), kThreads, 0, stream>>>(p);
+        ar_fused_kernel<<<grid_for(p.groups, info->sm_count, fused_blocks_per_sm()), kThreads, 0, stream>>>(p);
     } else if (phase == 1) {
         ar_push_kernel<<<grid_for(p.groups, info->sm_count), kThreads, 0, stream>>>(p);
     } else if (phase == 2) {
