@@ -127,8 +127,9 @@ int rdb_dense_gemm_fp8(const uint8_t *A, const uint8_t *B, const float *scale_a,
                        uint16_t *D, int M, int N, int K, void *stream);
 
 /* Tuner entry of the dense GEMM: tile_rows selects 128 x 256 or 256 x 256 output
- * tiles (0 = automatic), max_ctas caps the persistent grid (0 = one CTA per
- * SM).  The reference fixes its tiles with #defines (projects/
+ * tiles computed by one CTA (128, 256), or 256 x 256 tiles computed by pairs of
+ * CTAs (2; K must be a multiple of 128); 0 = automatic.  max_ctas caps the
+ * persistent grid (0 = one CTA per SM).  The reference fixes its tiles with #defines (projects/
  * async_gemm_16x16x64/core.cu:21-31) and retunes by recompiling (grid.py). */
 int rdb_dense_gemm_fp8_tuned(const uint8_t *A, const uint8_t *B, const float *scale_a, const float *scale_b,
                              uint16_t *D, int M, int N, int K, int tile_rows, int max_ctas, void *stream);

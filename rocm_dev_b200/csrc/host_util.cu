@@ -63,6 +63,21 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, 
     return r == CUDA_SUCCESS ? RDB_SUCCESS : RDB_CUDA_ERROR;
 }
 
+int make_tmap_kchunks(CUtensorMap* out, const void* base, uint64_t rows, uint64_t k_bytes, uint64_t pitch_bytes,
+                      uint32_t box_rows, uint32_t box_chunks) {
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return RDB_CUDA_ERROR;
+    if (k_bytes % 128 != 0) return RDB_BAD_SHAPE;
+    cuuint64_t dims[3] = {128, rows, k_bytes / 128};
+    cuuint64_t strides[2] = {pitch_bytes, 128};
+    cuuint32_t box[3] = {128, box_rows, box_chunks};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? RDB_SUCCESS : RDB_CUDA_ERROR;
+}
+
 }  // namespace rdb
 
 extern "C" {

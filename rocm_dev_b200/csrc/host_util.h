@@ -28,6 +28,12 @@ DeviceInfo* device_info(int* err);
 // Encodes a 2-D tiled tensor map over a row-major [rows, cols] array of
 // `elem_bytes`-sized elements with row pitch `pitch_bytes`.  box = {box_cols,
 // box_rows}.  swizzle is a CUtensorMapSwizzle value.
+// Byte matrix [rows][k_bytes] (k_bytes a multiple of 128) seen as [k_bytes/128][rows][128]: one box of
+// (128 B, box_rows, box_chunks) lands in shared memory as box_chunks consecutive K-major SWIZZLE_128B tiles
+// of box_rows rows - several k-blocks of an operand with a single TMA instruction.
+int make_tmap_kchunks(CUtensorMap* out, const void* base, uint64_t rows, uint64_t k_bytes, uint64_t pitch_bytes,
+                      uint32_t box_rows, uint32_t box_chunks);
+
 int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes, uint64_t rows,
                  uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swizzle,
                  CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B);

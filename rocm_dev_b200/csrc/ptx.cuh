@@ -176,6 +176,76 @@ __device__ __forceinline__ void tc_commit(uint32_t bar) {
                  : "memory");
 }
 
+// ------------------------------------------------- CTA pairs (cta_group::2)
+// Two CTAs of a cluster (ranks 2i and 2i+1) act as one MMA unit: the even CTA
+// issues 256-row MMAs that read A and half of B from each CTA's shared memory
+// and accumulate into each CTA's own TMEM.  Allocation, MMA and commit carry
+// the cta_group::2 qualifier; `*_cluster` addresses come from mapa_smem.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {       // one warp in EACH CTA
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// 2-D tiled load into this CTA's shared memory that reports its bytes to an
+// mbarrier of either CTA of the pair (a shared::cluster address).  No multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const CUtensorMap* tm, int x, int y,
+                                                 uint32_t bar_cluster, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3}], [%4], %5;"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(bar_cluster), "l"(policy)
+        : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_pair(uint32_t dst_smem, const CUtensorMap* tm, int x, int y, int z,
+                                                 uint32_t bar_cluster, uint64_t policy) {
+    asm volatile(
+        "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint"
+        " [%0], [%1, {%2, %3, %4}], [%5], %6;"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tm)), "r"(x), "r"(y), "r"(z), "r"(bar_cluster), "l"(policy)
+        : "memory");
+}
+// D[tmem of both CTAs] (+)= A * B^T, one 256 x N x 32 fp8 step issued by the even CTA.
+__device__ __forceinline__ void tc_mma_f8_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                               bool accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(static_cast<uint32_t>(accumulate))
+        : "memory");
+}
+// Arrive on one mbarrier (of either CTA) once all pair MMAs issued so far have finished.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster)
+                 : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+// Bounded wait with cluster-scope acquire (the arrivals come from the other CTA of a pair).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity) {
+    uint32_t spins = 0;
+    uint64_t t0 = 0;
+    while (true) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if (++spins == 2048) t0 = globaltimer_ns();
+        if (spins > 2048 && (spins & 0x3FF) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) return false;
+    }
+}
+
 // Shared-memory matrix descriptor for a K-major operand tile whose rows are
 // 128 bytes, written by TMA with SWIZZLE_128B: 8-row groups are 1024 bytes
 // apart (stride byte offset), descriptor version 1, layout type 2.

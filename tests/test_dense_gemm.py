@@ -54,6 +54,34 @@ def test_both_tile_heights(cuda_device, oracle, tile_rows, M, N, K):
     check_gemm_parity(bf16_bits(out), ref, ref64, mag, K)
 
 
+@pytest.mark.parametrize("max_ctas", [2, 0])
+@pytest.mark.parametrize("M,N,K", [(512, 512, 1024), (300, 520, 384), (1280, 768, 512), (257, 255, 128), (100, 40, 256)])
+def test_cta_pairs(cuda_device, oracle, max_ctas, M, N, K):
+    """256 x 256 tiles computed by pairs of CTAs (forced: the automatic choice skips shapes with this much
+    padding); max_ctas=2 makes a single pair walk every tile, alternating both accumulators."""
+    import rocm_dev_b200 as R
+    Aq, Bq, sa, sb = _operands(M, N, K, seed=13)
+    dev = cuda_device
+    out = R.dense_gemm_fp8(Aq.to(dev), Bq.to(dev), sa.to(dev), sb.to(dev), tile_rows=2, max_ctas=max_ctas)
+    torch.cuda.synchronize()
+    assert R.lib().rdb_device_status() == 0
+    ref = oracle.gemm_fp8_bf16(Aq.numpy(), Bq.numpy(), sa.item(), sb.item())
+    ref64, mag = oracle.gemm_fp8_f64(Aq.numpy(), Bq.numpy(), sa.item(), sb.item())
+    check_gemm_parity(bf16_bits(out), ref, ref64, mag, K)
+    # the pair kernel and the single-CTA kernel accumulate in the same order: identical bits
+    single = R.dense_gemm_fp8(Aq.to(dev), Bq.to(dev), sa.to(dev), sb.to(dev), tile_rows=128)
+    assert torch.equal(out, single)
+
+
+def test_cta_pairs_reject_k_not_multiple_of_128(cuda_device):
+    import rocm_dev_b200 as R
+    dev = cuda_device
+    A = torch.zeros((256, 272), dtype=torch.uint8, device=dev)
+    one = torch.ones(1, device=dev)
+    with pytest.raises(Exception):
+        R.dense_gemm_fp8(A, A, one, one, tile_rows=2)
+
+
 def test_many_tiles_per_cta_and_both_accumulators(cuda_device, oracle):
     # 40 x 12 = 480 tiles on 148 CTAs: every CTA runs 3-4 tiles, alternating accumulators
     _check_bf16(oracle, cuda_device, 5120, 3072, 256, seed=5)
