@@ -399,12 +399,15 @@ def bench_allreduce(torch, dist, R, dev, rank, world):
         t_fp8 = timed(lambda: ar.all_reduce(x, out=y), iters)
         t_nccl = timed(lambda: dist.all_reduce(z), iters)
         t_ws = timed(lambda: ar.all_reduce_in_workspace(x), iters)     # two-shot, result left in the workspace
+        t_v2 = timed(lambda: ar.all_reduce(x, out=y, algo=3), iters)   # second variant: FP8 all-gather (one more quantisation)
         S, f = n * 2, 2 * (world - 1) / world
         out["cases"][f"T{T}"] = {"bytes": S, "fp8_us": round(t_fp8 * 1e6, 2), "nccl_bf16_us": round(t_nccl * 1e6, 2),
                                  "fp8_in_workspace_us": round(t_ws * 1e6, 2),
                                  "fp8_in_workspace_busbw": round(S / t_ws * f / 1e9, 1),
                                  "fp8_busbw": round(S / t_fp8 * f / 1e9, 1), "nccl_bf16_busbw": round(S / t_nccl * f / 1e9, 1),
-                                 "ratio": round(t_nccl / t_fp8, 3)}
+                                 "ratio": round(t_nccl / t_fp8, 3),
+                                 "fp8_gather_variant_us": round(t_v2 * 1e6, 2), "fp8_gather_variant_busbw": round(S / t_v2 * f / 1e9, 1),
+                                 "fp8_gather_variant_ratio": round(t_nccl / t_v2, 3)}
     if R.lib().rdb_device_status() != 0:
         out["error"] = "device status word reports a timed-out wait"
     ar.close()

@@ -213,11 +213,14 @@ int rdb_ar_destroy(void *ctx);
 int rdb_ar_set_multicast(void *ctx, void *multicast_workspace);
 
 /* Collective: every rank calls it with the same n (a multiple of 128, at most
- * max_elems) and algo (0 automatic, 1 one-shot: every rank receives and
- * reduces everything, n <= 2^20; 2 two-shot: FP8 reduce-scatter then bf16
- * all-gather).  x, out: device pointers to n bf16.  out may be NULL for the
- * two-shot algorithm: the result then stays in the workspace (rdb_ar_result)
- * until this rank's next call. */
+ * max_elems) and algo (0 automatic: 1 or 2 by size; 1 one-shot: every rank
+ * receives and reduces everything, n <= 2^20; 2 two-shot: FP8 reduce-scatter
+ * then bf16 all-gather; 3 two-shot with an FP8 all-gather: the reduced bf16
+ * shard is block-quantised a second time before it travels, so the result is
+ * decode(encode(result of algo 2)) - fewer bytes on the wire, one more
+ * quantisation error; never chosen automatically).  x, out: device pointers to
+ * n bf16.  out may be NULL for algo 2: the result then stays in the workspace
+ * (rdb_ar_result) until this rank's next call. */
 int rdb_ar_allreduce(void *ctx, const uint16_t *x, uint16_t *out, size_t n, int algo, void *stream);
 const uint16_t *rdb_ar_result(void *ctx);
 

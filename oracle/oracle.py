@@ -166,6 +166,19 @@ def allreduce_fp8(xs_bf16):
     return out, q, s
 
 
+def allreduce_fp8_regather(xs_bf16):
+    """Second variant of the allreduce (FP8 all-gather): the bf16 result of
+    `allreduce_fp8` is block-quantised once more and decoded,
+    out = bf16(fp32(code) * scale).  No reference counterpart (the allreduce is
+    specified by configuration text only); defined here as the composition of
+    the two primitives above."""
+    y, _, _ = allreduce_fp8(xs_bf16)
+    q, s = quantize_blocks128(y)
+    dec = e4m3fn_decode(np.arange(256, dtype=np.uint8))
+    prod = dec[q].astype(np.float32) * np.repeat(s.astype(np.float32), 128)
+    return bf16_encode(prod.astype(np.float32))
+
+
 # --------------------------------------------------------------- 2:4 sparse
 def prune_2of4(W) -> np.ndarray:
     W = np.array(W, dtype=np.float32, order="C", copy=True)

@@ -17,6 +17,7 @@ from ._lib import check, lib
 
 GROUP = 512          # elements per unit of ownership (4 blocks of 128)
 ONE_SHOT, TWO_SHOT, AUTO = 1, 2, 0
+TWO_SHOT_FP8_GATHER = 3   # all-gather re-encoded in FP8: result = decode(encode(two-shot result)); opt-in
 
 
 def shard_groups(n: int, world: int):

@@ -64,7 +64,8 @@ struct Layout {
     size_t slot_groups;   // groups one source rank may push into one slot
     size_t off_q;         // [2][W][slot_groups * 512] bytes   (two sets, used alternately: set = epoch & 1)
     size_t off_s;         // [2][W][slot_groups * 4] floats
-    size_t off_gather;    // [max_elems] bf16
+    size_t off_gather;    // [max_elems] bf16; the FP8 all-gather uses it as [max_elems] codes + scales at gather_scale_off
+    size_t gather_scale_off;   // relative to off_gather
     size_t off_flags;     // [2 phases][2 epoch parities][kMaxWorld] uint32 epochs, then 4 block counters at word 64
     size_t bytes;
 };
@@ -80,6 +81,7 @@ static Layout make_layout(int world, size_t max_elems) {
     L.off_q = 0;
     L.off_s = round_up(L.off_q + 2 * static_cast<size_t>(world) * L.slot_groups * kGroup, 256);
     L.off_gather = round_up(L.off_s + 2 * static_cast<size_t>(world) * L.slot_groups * 4 * sizeof(float), 256);
+    L.gather_scale_off = groups * kGroup;
     L.off_flags = round_up(L.off_gather + groups * kGroup * 2, 256);
     L.bytes = L.off_flags + 1024;
     return L;
@@ -104,6 +106,7 @@ struct KParams {
     size_t groups;       // ceil(n / 512)
     unsigned epoch;
     int one_shot;
+    int fp8_gather;      // two-shot only: the all-gather carries re-encoded FP8 blocks instead of bf16
     int push_order;
     const __nv_bfloat16* x;
     __nv_bfloat16* out;  // may be nullptr (two-shot: result stays in the gather area)
@@ -335,14 +338,31 @@ __device__ __forceinline__ void reduce_body(const KParams& p, bool arrived) {
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const size_t e0 = g * kGroup + 256 * h + static_cast<size_t>(lane) * 8;
-            if (e0 >= p.n) continue;
+            const bool live = e0 < p.n;
             uint32_t o[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const __nv_bfloat162 b = __floats2bfloat162_rn(acc[h][2 * i], acc[h][2 * i + 1]);
-                o[i] = *reinterpret_cast<const uint32_t*>(&b);
+                o[i] = live ? *reinterpret_cast<const uint32_t*>(&b) : 0u;
             }
             const uint4 val = make_uint4(o[0], o[1], o[2], o[3]);
+            if (p.fp8_gather) {
+                // second variant: the bf16 result is block-quantised once more (same encoder, all 32
+                // lanes take part in the block maximum) and travels as 8 code bytes per lane plus one
+                // scale per 128 elements; every rank decodes it in phase 3
+                float s;
+                const uint2 q = encode8(val, s);
+                if (!live) continue;
+                for (int i = 0; i < p.world; i++) {
+                    int peer = p.rank + 1 + i;
+                    if (peer >= p.world) peer -= p.world;
+                    uint8_t* gq = p.ws[peer] + p.L.off_gather;
+                    *reinterpret_cast<uint2*>(gq + e0) = q;
+                    if ((lane & 15) == 0) reinterpret_cast<float*>(gq + p.L.gather_scale_off)[e0 / 128] = s;
+                }
+                continue;
+            }
+            if (!live) continue;
             if (p.one_shot) {
                 *reinterpret_cast<uint4*>(p.out + e0) = val;
             } else if (p.mc) {
@@ -366,6 +386,27 @@ __global__ void __launch_bounds__(kThreads) ar_reduce_kernel(const KParams p) {
 // ------------------------------------------------------------------ phase 3
 __device__ __forceinline__ void copy_out_body(const KParams& p) {
     if (p.out == nullptr) return;
+    if (p.fp8_gather) {
+        // decode: out = bf16(fp32(code) * block scale), 8 elements per thread
+        const uint8_t* gq = p.ws[p.rank] + p.L.off_gather;
+        const float* gs = reinterpret_cast<const float*>(gq + p.L.gather_scale_off);
+        const size_t n8 = p.n / 8;
+        for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < n8;
+             i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+            const uint2 q = __ldcg(reinterpret_cast<const uint2*>(gq) + i);
+            const float s = __ldcg(gs + i / 16);
+            float v[8];
+            decode8(q, v);
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const __nv_bfloat162 b = __floats2bfloat162_rn(__fmul_rn(v[2 * j], s), __fmul_rn(v[2 * j + 1], s));
+                o[j] = *reinterpret_cast<const uint32_t*>(&b);
+            }
+            reinterpret_cast<uint4*>(p.out)[i] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        return;
+    }
     const uint4* src = reinterpret_cast<const uint4*>(p.ws[p.rank] + p.L.off_gather);
     uint4* dst = reinterpret_cast<uint4*>(p.out);
     const size_t n16 = p.n / 8;
@@ -484,6 +525,7 @@ static int run_phase(Ctx* c, int phase, const uint16_t* x, uint16_t* out, size_t
     p.groups = (n + kGroup - 1) / kGroup;
     p.epoch = epoch;
     p.one_shot = algo == 1 ? 1 : 0;
+    p.fp8_gather = algo == 3 ? 1 : 0;
     p.push_order = c->push_order;
     p.x = reinterpret_cast<const __nv_bfloat16*>(x);
     p.out = reinterpret_cast<__nv_bfloat16*>(out);
@@ -509,8 +551,8 @@ static int check_call(Ctx* c, const uint16_t* x, uint16_t* out, size_t n, int& a
     if (!aligned16(x) || (out && !aligned16(out))) return RDB_BAD_ALIGNMENT;
     if (algo == 0) algo = (n <= kOneShotMaxElems / 4) ? 1 : 2;
     if (algo == 1 && n > kOneShotMaxElems) return RDB_SIZE_ABOVE_LIMIT;
-    if (algo == 1 && out == nullptr) return RDB_INVALID_CONFIG;
-    if (algo != 1 && algo != 2) return RDB_INVALID_CONFIG;
+    if ((algo == 1 || algo == 3) && out == nullptr) return RDB_INVALID_CONFIG;
+    if (algo < 1 || algo > 3) return RDB_INVALID_CONFIG;
     return RDB_SUCCESS;
 }
 

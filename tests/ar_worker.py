@@ -27,7 +27,7 @@ def main():
     print(f"rank {rank} backend {ar.backend} multicast {ar.multicast}")
     dev = torch.device("cuda", rank)
     cases = [(128, 1), (8192, 1), (8192, 2), (16 * 8192, 0), (128 * 8192, 2), (640, 2), (1024 * 8192, 0), (4096 * 8192, 2),
-             (513 * 8192 + 128, 2)]
+             (513 * 8192 + 128, 2), (640, 3), (128 * 8192, 3), (513 * 8192 + 128, 3)]
     for n, algo in cases:
         for rep in range(2):                 # twice: both staging sets, growing epochs
             xs = [torch.randn(n, generator=torch.Generator().manual_seed(1000 * rep + 17 * r + n)).bfloat16()
@@ -36,7 +36,7 @@ def main():
             torch.cuda.synchronize()
             assert R.lib().rdb_device_status() == 0, "device-side wait timed out"
             bits = np.stack([x.view(torch.int16).numpy().view(np.uint16) for x in xs])
-            want, _, _ = O.allreduce_fp8(bits)
+            want = O.allreduce_fp8_regather(bits) if algo == 3 else O.allreduce_fp8(bits)[0]
             got = out.cpu().view(torch.int16).numpy().view(np.uint16)
             assert np.array_equal(got, want), f"rank {rank} n {n} algo {algo} rep {rep}: {(got != want).sum()} differ"
             if algo == 2:                    # the same result left in the workspace (no copy-out)

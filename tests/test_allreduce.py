@@ -146,6 +146,50 @@ def test_emulated_ranks_on_one_gpu(cuda_device, oracle, world, algo):
         lr.close()
 
 
+def test_regather_variant_oracle_properties(oracle):
+    """The FP8-all-gather variant is decode(encode(first variant)): idempotent
+    (a second round trip changes nothing), exact on zero blocks, and within one
+    e4m3 rounding step (2^-4 relative to the block maximum's binade) of the first variant."""
+    n = 128 * 9
+    xs = np.stack([_bits(torch.randn(n, generator=torch.Generator().manual_seed(r)).bfloat16()) for r in range(4)])
+    xs[:, :128] = 0
+    v1, _, _ = oracle.allreduce_fp8(xs)
+    v2 = oracle.allreduce_fp8_regather(xs)
+    assert not v2[:128].any()
+    q, s = oracle.quantize_blocks128(v2)
+    again = oracle.bf16_encode(oracle.e4m3fn_decode(q).astype(np.float32) * np.repeat(s, 128))
+    assert np.array_equal(again, v2)
+    a, b = oracle.bf16_decode(v1).reshape(-1, 128), oracle.bf16_decode(v2).reshape(-1, 128)
+    amax = np.abs(a).max(axis=1, keepdims=True)
+    assert (np.abs(a - b) <= amax / 16 + 1e-30).all()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_emulated_ranks_fp8_all_gather_variant(cuda_device, oracle, world):
+    """algo 3: the reduced shard is block-quantised again for the all-gather;
+    bit-exact against the oracle's composition of the same primitives."""
+    import rocm_dev_b200 as R
+    from rocm_dev_b200.allreduce import TWO_SHOT_FP8_GATHER
+    lr = R.LocalRanks(world, max_elems=1 << 20, device=cuda_device)
+    try:
+        for n in (128, 640, 128 * 517, 1 << 20):
+            for rep in range(2):
+                xs = [torch.randn(n, generator=torch.Generator().manual_seed(7 * rep + r)).bfloat16() * (1 + 10 * r) for r in range(world)]
+                outs = lr.all_reduce([x.to(cuda_device) for x in xs], algo=TWO_SHOT_FP8_GATHER)
+                torch.cuda.synchronize()
+                assert R.lib().rdb_device_status() == 0
+                want = oracle.allreduce_fp8_regather(np.stack([_bits(x) for x in xs]))
+                for r in range(world):
+                    assert np.array_equal(_bits(outs[r]), want), (world, n, rep, r)
+                # a first-variant call in between must still be exact (the two share the gather area)
+                outs = lr.all_reduce([x.to(cuda_device) for x in xs], algo=2)
+                want1, _, _ = oracle.allreduce_fp8(np.stack([_bits(x) for x in xs]))
+                assert np.array_equal(_bits(outs[0]), want1)
+    finally:
+        lr.close()
+
+
 @pytest.mark.gpu
 def test_full_size_properties(cuda_device, oracle):
     """64 MB per rank (T = 4096 rows of 8192): close to the exact sum, identical
