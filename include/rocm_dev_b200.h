@@ -211,6 +211,12 @@ int rdb_ar_destroy(void *ctx);
  * algorithm then uses multimem.st (one store reaches all ranks).  NULL switches
  * back to per-peer stores.  Every rank must make the same choice. */
 int rdb_ar_set_multicast(void *ctx, void *multicast_workspace);
+/* Diagnostics: registers a device buffer of 16 uint64.  While registered, each
+ * rdb_ar_allreduce call stores %globaltimer stamps of its first CTA in words
+ * 0-5 (entry, own pushes issued, all ranks' pushes arrived, own reduction and
+ * all-gather stores issued, all ranks' gathers arrived, exit) and of its last
+ * CTA in words 8-13.  NULL switches it off.  No reference counterpart. */
+int rdb_ar_set_trace(void *ctx, unsigned long long *device_buffer16);
 
 /* Collective: every rank calls it with the same n (a multiple of 128, at most
  * max_elems) and algo (0 automatic: 1 or 2 by size; 1 one-shot: every rank

@@ -46,6 +46,7 @@ _SIGNATURES = {
     "rdb_ar_create": (i, [i, i, C.POINTER(C.c_void_p), C.c_size_t, C.POINTER(C.c_void_p)]),
     "rdb_ar_destroy": (i, [vp]),
     "rdb_ar_set_multicast": (i, [vp, vp]),
+    "rdb_ar_set_trace": (i, [vp, vp]),
     "rdb_ar_allreduce": (i, [vp, vp, vp, C.c_size_t, i, vp]),
     "rdb_ar_result": (C.c_void_p, [vp]),
     "rdb_ar_begin_call": (i, [vp]),

@@ -95,6 +95,7 @@ struct Ctx {
     uint8_t* mc;          // optional NVLS multicast alias of the workspace (same layout), else nullptr
     unsigned epoch;
     int push_order;       // 0 linear, 1 rotated by rank, 2 owner-interleaved (default)
+    unsigned long long* trace;   // optional: 8 globaltimer stamps of the last fused call (diagnostics)
 };
 
 struct KParams {
@@ -111,6 +112,7 @@ struct KParams {
     const __nv_bfloat16* x;
     __nv_bfloat16* out;  // may be nullptr (two-shot: result stays in the gather area)
     int* status;
+    unsigned long long* trace;
 };
 
 __device__ __forceinline__ size_t group_begin(int r, size_t groups, int world) { return groups * r / world; }
@@ -177,6 +179,19 @@ __device__ __forceinline__ void decode8(const uint2 q, float* v) {
             v[4 * i + 2 * h + 1] = f.y;
         }
     }
+}
+
+// The 512 code bytes of a group: lane l holds bytes [8 l, 8 l + 8) of each 256-byte half
+// (q[0], q[1]).  Returns them regrouped so that lane l holds bytes [16 l, 16 l + 16) of the
+// group: remote stores of 16 bytes per lane (512 contiguous bytes per warp instruction) move
+// over NVLink markedly faster than 8-byte ones.
+__device__ __forceinline__ uint4 regroup16(const uint2* q, int lane) {
+    const int src = (lane & 15) * 2;
+    const uint32_t a0 = __shfl_sync(0xffffffffu, q[0].x, src), a1 = __shfl_sync(0xffffffffu, q[0].y, src);
+    const uint32_t a2 = __shfl_sync(0xffffffffu, q[0].x, src + 1), a3 = __shfl_sync(0xffffffffu, q[0].y, src + 1);
+    const uint32_t b0 = __shfl_sync(0xffffffffu, q[1].x, src), b1 = __shfl_sync(0xffffffffu, q[1].y, src);
+    const uint32_t b2 = __shfl_sync(0xffffffffu, q[1].x, src + 1), b3 = __shfl_sync(0xffffffffu, q[1].y, src + 1);
+    return lane < 16 ? make_uint4(a0, a1, a2, a3) : make_uint4(b0, b1, b2, b3);
 }
 
 // Work item of every kernel below: one warp per 512-element group, handled as
@@ -288,11 +303,10 @@ __device__ __forceinline__ void push_body(const KParams& p) {
         // the four block scales of the group: (half 0: lanes 0, 16), (half 1: lanes 0, 16)
         const float s1 = __shfl_sync(0xffffffffu, s[0], 16), s3 = __shfl_sync(0xffffffffu, s[1], 16);
         const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + p.rank) * p.L.slot_groups + slot_g;
+        const uint4 q16 = regroup16(q, lane);
         for (int peer = first; peer <= last; peer++) {
             uint8_t* base = p.ws[peer];
-            uint2* dq = reinterpret_cast<uint2*>(base + p.L.off_q + slot * kGroup) + lane;
-            dq[0] = q[0];
-            dq[32] = q[1];
+            reinterpret_cast<uint4*>(base + p.L.off_q + slot * kGroup)[lane] = q16;
             if (lane == 0) {
                 float4* ds = reinterpret_cast<float4*>(base + p.L.off_s) + slot;
                 *ds = make_float4(s[0], s1, s[1], s3);
@@ -335,43 +349,50 @@ __device__ __forceinline__ void reduce_body(const KParams& p, bool arrived) {
 #pragma unroll
             for (int i = 0; i < 8; i++) acc[1][i] = __fadd_rn(acc[1][i], __fmul_rn(v[i], s1));
         }
+        uint4 val[2];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            const size_t e0 = g * kGroup + 256 * h + static_cast<size_t>(lane) * 8;
-            const bool live = e0 < p.n;
+            const bool live = g * kGroup + 256 * h + static_cast<size_t>(lane) * 8 < p.n;
             uint32_t o[4];
 #pragma unroll
             for (int i = 0; i < 4; i++) {
                 const __nv_bfloat162 b = __floats2bfloat162_rn(acc[h][2 * i], acc[h][2 * i + 1]);
                 o[i] = live ? *reinterpret_cast<const uint32_t*>(&b) : 0u;
             }
-            const uint4 val = make_uint4(o[0], o[1], o[2], o[3]);
-            if (p.fp8_gather) {
-                // second variant: the bf16 result is block-quantised once more (same encoder, all 32
-                // lanes take part in the block maximum) and travels as 8 code bytes per lane plus one
-                // scale per 128 elements; every rank decodes it in phase 3
-                float s;
-                const uint2 q = encode8(val, s);
-                if (!live) continue;
-                for (int i = 0; i < p.world; i++) {
-                    int peer = p.rank + 1 + i;
-                    if (peer >= p.world) peer -= p.world;
-                    uint8_t* gq = p.ws[peer] + p.L.off_gather;
-                    *reinterpret_cast<uint2*>(gq + e0) = q;
-                    if ((lane & 15) == 0) reinterpret_cast<float*>(gq + p.L.gather_scale_off)[e0 / 128] = s;
-                }
-                continue;
+            val[h] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+        if (p.fp8_gather) {
+            // second variant: the bf16 result is block-quantised once more (same encoder) and travels as
+            // 512 code bytes plus four scales per group; every rank decodes it in phase 3.  Blocks past
+            // the end of the vector are zeros and land in the padding of the gather area.
+            uint2 q[2];
+            float sc[2];
+#pragma unroll
+            for (int h = 0; h < 2; h++) q[h] = encode8(val[h], sc[h]);
+            const float s1 = __shfl_sync(0xffffffffu, sc[0], 16), s3 = __shfl_sync(0xffffffffu, sc[1], 16);
+            const uint4 q16 = regroup16(q, lane);
+            for (int i = 0; i < p.world; i++) {
+                int peer = p.rank + 1 + i;
+                if (peer >= p.world) peer -= p.world;
+                uint8_t* gq = p.ws[peer] + p.L.off_gather;
+                reinterpret_cast<uint4*>(gq + g * kGroup)[lane] = q16;
+                if (lane == 0) reinterpret_cast<float4*>(gq + p.L.gather_scale_off)[g] = make_float4(sc[0], s1, sc[1], s3);
             }
-            if (!live) continue;
+            continue;
+        }
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const size_t e0 = g * kGroup + 256 * h + static_cast<size_t>(lane) * 8;
+            if (e0 >= p.n) continue;
             if (p.one_shot) {
-                *reinterpret_cast<uint4*>(p.out + e0) = val;
+                *reinterpret_cast<uint4*>(p.out + e0) = val[h];
             } else if (p.mc) {
-                multimem_st_v4(p.mc + p.L.off_gather + e0 * 2, val);
+                multimem_st_v4(p.mc + p.L.off_gather + e0 * 2, val[h]);
             } else {
                 for (int i = 0; i < p.world; i++) {
                     int peer = p.rank + 1 + i;
                     if (peer >= p.world) peer -= p.world;
-                    *reinterpret_cast<uint4*>(p.ws[peer] + p.L.off_gather + e0 * 2) = val;
+                    *reinterpret_cast<uint4*>(p.ws[peer] + p.L.off_gather + e0 * 2) = val[h];
                 }
             }
         }
@@ -427,13 +448,29 @@ __global__ void __launch_bounds__(kThreads) ar_gather_kernel(const KParams p) {
 // All CTAs must be resident together (the grid is capped accordingly), because
 // early CTAs wait for the last one.  Not usable when several ranks share one
 // GPU: that case uses the three separate launches above.
+// Diagnostics: block 0 and the last block stamp %globaltimer after each step.
+__device__ __forceinline__ void stamp(const KParams& p, int slot) {
+    if (p.trace && threadIdx.x == 0) {
+        if (blockIdx.x == 0) p.trace[slot] = globaltimer_ns();
+        if (blockIdx.x == gridDim.x - 1) p.trace[8 + slot] = globaltimer_ns();
+    }
+}
+
 __global__ void __launch_bounds__(kThreads, kBlocksPerSm) ar_fused_kernel(const KParams p) {
+    stamp(p, 0);
     push_body(p);
+    stamp(p, 1);
     publish_when_grid_done(p, 0);
-    reduce_body(p, wait_flags(p, 0));
+    const bool arrived = wait_flags(p, 0);
+    stamp(p, 2);
+    reduce_body(p, arrived);
+    stamp(p, 3);
     if (p.one_shot) return;
     publish_when_grid_done(p, 1);
-    if (wait_flags(p, 1)) copy_out_body(p);
+    const bool gathered = wait_flags(p, 1);
+    stamp(p, 4);
+    if (gathered) copy_out_body(p);
+    stamp(p, 5);
 }
 
 // Standalone encoder (the quantise step alone, for bit-exact tests and callers
@@ -530,6 +567,7 @@ static int run_phase(Ctx* c, int phase, const uint16_t* x, uint16_t* out, size_t
     p.x = reinterpret_cast<const __nv_bfloat16*>(x);
     p.out = reinterpret_cast<__nv_bfloat16*>(out);
     p.status = info->status_dev;
+    p.trace = phase == 0 ? c->trace : nullptr;
     if (phase == 0) {
         ar_fused_kernel<<<grid_for(p.groups, info->sm_count, fused_blocks_per_sm()), kThreads, 0, stream>>>(p);
     } else if (phase == 1) {
@@ -601,6 +639,7 @@ int rdb_ar_create(int rank, int world, void* const* workspaces, size_t max_elems
     for (int i = 0; i < rdb::ar::kMaxWorld; i++) c->ws[i] = i < world ? static_cast<uint8_t*>(workspaces[i]) : nullptr;
     c->mc = nullptr;
     c->epoch = 0;
+    c->trace = nullptr;
     // tuning override for A/B measurements: RDB_AR_PUSH_ORDER = 0 (linear), 1 (rotated), 2 (interleaved, default)
     const char* po = getenv("RDB_AR_PUSH_ORDER");
     c->push_order = (po && po[0] >= '0' && po[0] <= '2' && !po[1]) ? po[0] - '0' : 2;
@@ -613,6 +652,13 @@ int rdb_ar_set_multicast(void* ctx, void* multicast_workspace) {
     if (!c) return RDB_INVALID_CONFIG;
     if (multicast_workspace && !rdb::aligned16(multicast_workspace)) return RDB_BAD_ALIGNMENT;
     c->mc = static_cast<uint8_t*>(multicast_workspace);
+    return RDB_SUCCESS;
+}
+
+int rdb_ar_set_trace(void* ctx, unsigned long long* device_buffer16) {
+    rdb::ar::Ctx* c = static_cast<rdb::ar::Ctx*>(ctx);
+    if (!c) return RDB_INVALID_CONFIG;
+    c->trace = device_buffer16;
     return RDB_SUCCESS;
 }
 

@@ -215,6 +215,35 @@ def test_full_size_properties(cuda_device, oracle):
 
 
 @pytest.mark.gpu
+def test_fused_call_on_one_rank_and_its_trace(cuda_device, oracle):
+    """World size 1 through the fused single-launch entry (the multi-rank form of
+    the same kernel runs in the multi-GPU tests), with the step trace switched on:
+    stamps are ordered and the result equals the oracle's."""
+    import rocm_dev_b200 as R
+    from rocm_dev_b200.allreduce import _Workspace, _create
+    from rocm_dev_b200._lib import check
+    n = 128 * 4099
+    with torch.cuda.device(cuda_device):
+        ws = _Workspace(1, n)
+        ctx = _create(0, 1, [ws.ptr], n)
+        trace = torch.zeros(16, dtype=torch.int64, device=cuda_device)
+        check(R.lib().rdb_ar_set_trace(ctx, trace.data_ptr()), "rdb_ar_set_trace")
+        x = torch.randn(n, generator=torch.Generator().manual_seed(5)).bfloat16()
+        xd, out = x.to(cuda_device), torch.empty(n, dtype=torch.bfloat16, device=cuda_device)
+        stream = torch.cuda.current_stream().cuda_stream
+        for algo, want in ((2, oracle.allreduce_fp8(_bits(x)[None])[0]), (3, oracle.allreduce_fp8_regather(_bits(x)[None]))):
+            check(R.lib().rdb_ar_allreduce(ctx, xd.data_ptr(), out.data_ptr(), n, algo, stream), "rdb_ar_allreduce")
+            torch.cuda.synchronize()
+            assert R.lib().rdb_device_status() == 0
+            assert np.array_equal(_bits(out), want)
+            t = trace.cpu().numpy()
+            assert (np.diff(t[:6]) >= 0).all() and t[0] > 0 and (np.diff(t[8:14]) >= 0).all()
+        check(R.lib().rdb_ar_set_trace(ctx, None), "rdb_ar_set_trace")
+        R.lib().rdb_ar_destroy(ctx)
+        ws.free()
+
+
+@pytest.mark.gpu
 def test_error_codes(cuda_device):
     import ctypes as C
     import rocm_dev_b200 as R
