@@ -263,17 +263,19 @@ def test_error_codes(cuda_device):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4])
 @pytest.mark.parametrize("backend", ["ipc", "auto"])
-def test_two_processes_two_gpus(cuda_device, backend):
+def test_one_process_per_gpu(cuda_device, backend, world):
     """Real peer-to-peer path: one process per GPU; workspaces shared by CUDA
     IPC, or allocated as symmetric memory (multimem all-gather where the
     allocation has a multicast address)."""
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
-    env = dict(os.environ, MASTER_ADDR="127.0.0.1", MASTER_PORT=str(29600 + os.getpid() % 300 + (7 if backend == "auto" else 0)),
-               WORLD_SIZE="2", RDB_AR_BACKEND=backend)
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    env = dict(os.environ, MASTER_ADDR="127.0.0.1",
+               MASTER_PORT=str(29600 + os.getpid() % 300 + (7 if backend == "auto" else 0) + world),
+               WORLD_SIZE=str(world), RDB_AR_BACKEND=backend)
     procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "ar_worker.py")], env=dict(env, RANK=str(r)),
-                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(2)]
+                              stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
     outs = [p.communicate(timeout=600)[0] for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(outs)
-    assert all(f"rank {r} ok" in outs[r] for r in range(2))
+    assert all(f"rank {r} ok" in outs[r] for r in range(world))
