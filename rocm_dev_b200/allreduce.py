@@ -107,9 +107,10 @@ class Fp8AllReduce:
             self.backend = "symm" if self.symm is not None else "ipc"
             self.ctx = _create(self.rank, self.world, ptrs, self.max_elems)
             if multimem is None:
-                # one multicast store replaces W-1 peer stores; measured slower than per-peer stores at
-                # 2 and 4 ranks and slightly faster at 8
-                multimem = self.world >= 8
+                # one multicast store replaces W-1 peer stores: measured slower than per-peer stores at 2
+                # and 4 ranks, 1.5 % faster at 8 ranks for 64 MiB but twice as slow there for 16 MiB with a
+                # copy-out - so it is opt-in
+                multimem = False
             if mc and multimem:
                 check(lib().rdb_ar_set_multicast(self.ctx, mc), "rdb_ar_set_multicast")
                 self.multicast = True
