@@ -208,40 +208,53 @@ __device__ __forceinline__ uint4 regroup16(const uint2* q, int lane) {
 // means a consumer launch never depends on a launch issued after it.
 __device__ __forceinline__ void publish_when_grid_done(const KParams& p, int which) {
     __syncthreads();
-    if (threadIdx.x == 0) {
-        __threadfence_system();
-        unsigned* cnt = reinterpret_cast<unsigned*>(p.ws[p.rank] + p.L.off_flags) + 64 + which * 2 + (p.epoch & 1u);   // two calls may be in flight
-        const unsigned old = atomicAdd(cnt, 1u);
-        if (old == gridDim.x - 1) {
-            *cnt = 0;                          // ready for the next launch
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        unsigned last = 0;
+        if (lane == 0) {
             __threadfence_system();
-            for (int peer = 0; peer < p.world; peer++) {
-                unsigned* f = reinterpret_cast<unsigned*>(p.ws[peer] + p.L.off_flags) + (which * 2 + (p.epoch & 1u)) * kMaxWorld + p.rank;
-                st_release_sys(f, p.epoch);
+            unsigned* cnt = reinterpret_cast<unsigned*>(p.ws[p.rank] + p.L.off_flags) + 64 + which * 2 + (p.epoch & 1u);   // two calls may be in flight
+            const unsigned old = atomicAdd(cnt, 1u);
+            if (old == gridDim.x - 1) {
+                *cnt = 0;                      // ready for the next launch
+                __threadfence_system();
+                last = 1;
             }
+        }
+        last = __shfl_sync(0xffffffffu, last, 0);
+        __syncwarp();
+        // one lane per peer: the W release stores travel concurrently
+        if (last && lane < p.world) {
+            unsigned* f = reinterpret_cast<unsigned*>(p.ws[lane] + p.L.off_flags) + (which * 2 + (p.epoch & 1u)) * kMaxWorld + p.rank;
+            st_release_sys(f, p.epoch);
         }
     }
 }
 
 // Every block waits (bounded) until all ranks have published `epoch` in row
-// `which` of this rank's flag block.  Returns false on timeout.
+// `which` of this rank's flag block; lane r of the first warp polls rank r's
+// word, so the W acquire loads overlap.  Returns false on timeout.
 __device__ __forceinline__ bool wait_flags(const KParams& p, int which) {
     __shared__ int ok_s;
-    if (threadIdx.x == 0) {
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
         // one flag row per epoch parity: two calls may be in flight and may finish out of order,
         // but calls of equal parity are ordered, so each word only ever grows
         const unsigned* mine = reinterpret_cast<const unsigned*>(p.ws[p.rank] + p.L.off_flags) + (which * 2 + (p.epoch & 1u)) * kMaxWorld;
         bool ok = true;
-        const uint64_t t0 = globaltimer_ns();
-        for (int r = 0; r < p.world && ok; r++) {
+        if (lane < p.world) {
+            const uint64_t t0 = globaltimer_ns();
             unsigned spins = 0;
             // epochs only grow; a flag at or beyond this call's epoch means "arrived"
-            while (static_cast<int>(ld_acquire_sys(mine + r) - p.epoch) < 0) {
+            while (static_cast<int>(ld_acquire_sys(mine + lane) - p.epoch) < 0) {
                 if ((++spins & 0xFF) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) { ok = false; break; }
             }
         }
-        if (!ok) report_timeout(p.status);
-        ok_s = ok ? 1 : 0;
+        ok = __all_sync(0xffffffffu, ok);
+        if (lane == 0) {
+            if (!ok) report_timeout(p.status);
+            ok_s = ok ? 1 : 0;
+        }
     }
     __syncthreads();
     return ok_s != 0;
