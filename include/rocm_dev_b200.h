@@ -244,8 +244,10 @@ int rdb_quantize_blocks128(const uint16_t *x, uint8_t *q, float *scales, size_t 
 
 /* Per-tensor quantiser, the step before every GEMM above: scale[0] = amax/448
  * (1 for an all-zero tensor), q[i] = e4m3fn_sat_rn(x[i] / scale[0]) for a bf16
- * vector x of n elements (device pointers; x 16-byte aligned).  One kernel;
- * bit-exact with the host rule.  The reference's drivers draw fp8 values
+ * vector x of n elements (device pointers; x 16-byte aligned).  One cooperative
+ * kernel; bit-exact with the host rule.  The maximum is combined in a small
+ * per-device scratch area owned by the library: calls on one device must be
+ * ordered (same stream, or otherwise serialised), not concurrent.  The reference's drivers draw fp8 values
  * directly (projects/common.cuh:97-105) and have no counterpart. */
 int rdb_quantize_per_tensor(const uint16_t *x, uint8_t *q, float *scale, size_t n, void *stream);
 

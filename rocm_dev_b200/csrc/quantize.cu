@@ -51,6 +51,21 @@ __device__ __forceinline__ uint2 encode8(const uint4 v, const rdb::ar::BlockDivi
     return make_uint2(o[0], o[1]);
 }
 
+// The last block to leave puts the barrier words and the maximum back to zero
+// for the next call (also after a timed-out barrier).
+__device__ __forceinline__ void leave(unsigned* scratch) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned left = atom_add_release_gpu(scratch + 1, 1u);
+        if (left == gridDim.x - 1) {
+            scratch[0] = 0;
+            scratch[1] = 0;
+            scratch[2] = 0;
+            __threadfence();
+        }
+    }
+}
+
 __global__ void __launch_bounds__(kThreads)
 quantize_per_tensor_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q, float* __restrict__ scale_out,
                            size_t n, unsigned* scratch, int* status) {
@@ -75,7 +90,7 @@ quantize_per_tensor_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restr
     if ((threadIdx.x & 31) == 0 && amax > 0.0f) atomicMax(scratch + 2, __float_as_uint(amax));   // non-negative floats order like uints
     if (!grid_barrier(scratch, gridDim.x)) {
         if (threadIdx.x == 0) report_timeout(status);
-        grid_barrier_exit(scratch, gridDim.x);
+        leave(scratch);
         return;
     }
     const float s = rdb::ar::block_scale(__uint_as_float(ld_acquire_gpu(scratch + 2)));
@@ -98,17 +113,7 @@ quantize_per_tensor_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restr
         const uint32_t one = static_cast<uint32_t>(reinterpret_cast<const uint16_t*>(x)[i]);
         q[i] = static_cast<uint8_t>(encode8(make_uint4(one, 0u, 0u, 0u), d).x & 0xFF);
     }
-    // everyone has read the maximum: the last block to leave clears it for the next call
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned left = atom_add_release_gpu(scratch + 1, 1u);
-        if (left == gridDim.x - 1) {
-            scratch[0] = 0;
-            scratch[1] = 0;
-            scratch[2] = 0;
-            __threadfence();
-        }
-    }
+    leave(scratch);   // everyone has read the maximum
 }
 
 static unsigned* scratch_words(int* err) {
