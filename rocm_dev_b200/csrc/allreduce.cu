@@ -600,7 +600,10 @@ static int check_call(Ctx* c, const uint16_t* x, uint16_t* out, size_t n, int& a
     if (n == 0 || n % 128 != 0) return RDB_BAD_SHAPE;
     if (n > c->max_elems) return RDB_SIZE_ABOVE_LIMIT;
     if (!aligned16(x) || (out && !aligned16(out))) return RDB_BAD_ALIGNMENT;
-    if (algo == 0) algo = (n <= kOneShotMaxElems / 4) ? 1 : 2;
+    // one-shot below 256 K elements; with two ranks it was measured faster up to its size limit
+    // (2 MiB of bf16: 14.9 us against 24.3 us two-shot and 19.0 us NCCL)
+    if (algo == 0)
+        algo = (out != nullptr && (n <= kOneShotMaxElems / 4 || (c->world == 2 && n <= kOneShotMaxElems))) ? 1 : 2;
     if (algo == 1 && n > kOneShotMaxElems) return RDB_SIZE_ABOVE_LIMIT;
     if ((algo == 1 || algo == 3) && out == nullptr) return RDB_INVALID_CONFIG;
     if (algo < 1 || algo > 3) return RDB_INVALID_CONFIG;
