@@ -416,17 +416,18 @@ def bench_allreduce(torch, dist, R, dev, rank, world):
 
 def run_single_other(args, torch, R, quant, dev):
     """Profiling aid for the other kernels: plain launches of one small case.
-    dense_<n> (n^3), sparse_M<m> (N=K=8192), reduce_<b>x<m>x<n>, quantize_T<t> ([t,8192] bf16, per-128 blocks), quantizept_T<t> (per tensor)."""
+    dense_<n> (n^3; densesingle_<n> for the single-CTA kernel), sparse_M<m> (N=K=8192), reduce_<b>x<m>x<n>, quantize_T<t> ([t,8192] bf16, per-128 blocks), quantizept_T<t> (per tensor)."""
     one = torch.ones(1, device=dev)
     kind, _, arg = args.single.partition("_")
     reps = args.warmup + args.steps
-    if kind == "dense":
+    if kind in ("dense", "densesingle"):          # densesingle: the single-CTA 256 x 256 kernel instead of CTA pairs
         n = int(arg)
+        tile_rows = 256 if kind == "densesingle" else 0
         A = torch.randint(0, 0x78, (n, n), dtype=torch.uint8, device=dev)
         B = torch.randint(0, 0x78, (n, n), dtype=torch.uint8, device=dev)
         D = torch.empty((n, n), dtype=torch.bfloat16, device=dev)
         for _ in range(reps):
-            R.dense_gemm_fp8(A, B, one, one, out=D)
+            R.dense_gemm_fp8(A, B, one, one, out=D, tile_rows=tile_rows)
         work = {"flops_per_launch": 2.0 * n ** 3}
     elif kind == "sparse":
         M, N, K = int(arg[1:]), 8192, 8192
