@@ -453,9 +453,15 @@ def run_single_other(args, torch, R, quant, dev):
     elif kind == "quantize":
         n = int(arg[1:]) * 8192
         x = torch.randn(n, device=dev).bfloat16()
-        for _ in range(reps):
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(2)]
+        for i in range(reps):
+            if i == args.warmup:
+                ev[0].record()
             R.quantize_blocks128(x)
-        work = {"algorithmic_bytes_per_launch": n * 2 + n + n // 32}
+        ev[1].record()
+        torch.cuda.synchronize()
+        us = ev[0].elapsed_time(ev[1]) * 1e3 / max(1, args.steps)
+        work = {"algorithmic_bytes_per_launch": n * 2 + n + n // 32, "us_per_launch": round(us, 2)}
     elif kind == "quantizept":
         n = int(arg[1:]) * 8192
         x = [torch.randn(n, device=dev).bfloat16() for _ in range(2)]
