@@ -506,7 +506,10 @@ static int run(const uint8_t* A, const uint8_t* B, const float* sa, const float*
     const bool want256 = tiles256 >= info->sm_count && pad_ok;
     if (tile_rows == 2 || (tile_rows == 0 && pad_ok && K % 128 == 0 && info->sm_count >= 2)) {
         if (K % 128 != 0) return RDB_INVALID_CONFIG;
-        return launch_pair<2>(A, B, sa, sb, D, out_f32, M, N, K, max_ctas, info, stream);
+        const int r = launch_pair<2>(A, B, sa, sb, D, out_f32, M, N, K, max_ctas, info, stream);
+        // a device or a partition that refuses the cluster launch: the automatic choice falls back to single CTAs
+        if (r != RDB_CUDA_ERROR || tile_rows == 2) return r;
+        cudaGetLastError();
     }
     const int rb = (tile_rows == 128 || (tile_rows == 0 && !want256)) ? 1 : 2;
     return rb == 1 ? launch<1>(A, B, sa, sb, D, out_f32, M, N, K, max_ctas, info, stream)
