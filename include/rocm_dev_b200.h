@@ -219,7 +219,7 @@ int rdb_ar_set_multicast(void *ctx, void *multicast_workspace);
 int rdb_ar_set_trace(void *ctx, unsigned long long *device_buffer16);
 
 /* Collective: every rank calls it with the same n (a multiple of 128, at most
- * max_elems) and algo (0 automatic: one-shot up to 2^18 elements - up to 2^20
+ * max_elems) and algo (0 automatic: one-shot up to 2^19 elements - up to 2^20
  * with two ranks - when out is given, else two-shot; 1 one-shot: every rank
  * receives and reduces everything, n <= 2^20; 2 two-shot: FP8 reduce-scatter
  * then bf16 all-gather; 3 two-shot with an FP8 all-gather: the reduced bf16

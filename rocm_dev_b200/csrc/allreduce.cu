@@ -600,10 +600,10 @@ static int check_call(Ctx* c, const uint16_t* x, uint16_t* out, size_t n, int& a
     if (n == 0 || n % 128 != 0) return RDB_BAD_SHAPE;
     if (n > c->max_elems) return RDB_SIZE_ABOVE_LIMIT;
     if (!aligned16(x) || (out && !aligned16(out))) return RDB_BAD_ALIGNMENT;
-    // one-shot below 256 K elements; with two ranks it was measured faster up to its size limit
-    // (2 MiB of bf16: 14.9 us against 24.3 us two-shot and 19.0 us NCCL)
+    // one-shot up to 512 K elements (8 ranks, 1 MiB of bf16: 24.0 us against 26.6 us two-shot; at 2 MiB 32.2 against
+    // 29.6); with two ranks up to its size limit (2 MiB: 14.9 us against 24.3 us two-shot and 19.0 us NCCL)
     if (algo == 0)
-        algo = (out != nullptr && (n <= kOneShotMaxElems / 4 || (c->world == 2 && n <= kOneShotMaxElems))) ? 1 : 2;
+        algo = (out != nullptr && (n <= kOneShotMaxElems / 2 || (c->world == 2 && n <= kOneShotMaxElems))) ? 1 : 2;
     if (algo == 1 && n > kOneShotMaxElems) return RDB_SIZE_ABOVE_LIMIT;
     if ((algo == 1 || algo == 3) && out == nullptr) return RDB_INVALID_CONFIG;
     if (algo < 1 || algo > 3) return RDB_INVALID_CONFIG;

@@ -23,7 +23,13 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
     import rocm_dev_b200 as R
     from oracle import oracle as O
-    ar = R.Fp8AllReduce(max_elems=4096 * 8192, backend=backend)
+    try:
+        ar = R.Fp8AllReduce(max_elems=4096 * 8192, backend=backend)
+    except Exception as e:  # noqa: BLE001  - no symmetric memory in this build of torch: the IPC workspace is the fallback
+        if backend != "symm":
+            raise
+        print(f"rank {rank}: symmetric memory unavailable ({type(e).__name__}), using ipc")
+        ar = R.Fp8AllReduce(max_elems=4096 * 8192, backend="ipc")
     print(f"rank {rank} backend {ar.backend} multicast {ar.multicast}")
     dev = torch.device("cuda", rank)
     cases = [(128, 1), (8192, 1), (8192, 2), (16 * 8192, 0), (128 * 8192, 2), (640, 2), (1024 * 8192, 0), (4096 * 8192, 2),

@@ -264,7 +264,7 @@ def test_error_codes(cuda_device):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("world", [2, 4])
-@pytest.mark.parametrize("backend", ["ipc", "auto"])
+@pytest.mark.parametrize("backend", ["ipc", "symm"])
 def test_one_process_per_gpu(cuda_device, backend, world):
     """Real peer-to-peer path: one process per GPU; workspaces shared by CUDA
     IPC, or allocated as symmetric memory (multimem all-gather where the
@@ -272,7 +272,7 @@ def test_one_process_per_gpu(cuda_device, backend, world):
     if torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} GPUs")
     env = dict(os.environ, MASTER_ADDR="127.0.0.1",
-               MASTER_PORT=str(29600 + os.getpid() % 300 + (7 if backend == "auto" else 0) + world),
+               MASTER_PORT=str(29600 + os.getpid() % 300 + (7 if backend == "symm" else 0) + world),
                WORLD_SIZE=str(world), RDB_AR_BACKEND=backend)
     procs = [subprocess.Popen([sys.executable, os.path.join(ROOT, "tests", "ar_worker.py")], env=dict(env, RANK=str(r)),
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True) for r in range(world)]
