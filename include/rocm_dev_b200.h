@@ -52,6 +52,14 @@ const char *rdb_status_string(int status);
  * since the last call (RDB_SUCCESS if none) and clears it. */
 int rdb_device_status(void);
 
+/* Time budget of every bounded device-side wait on the CURRENT device, in
+ * nanoseconds (default 10^9).  Synchronises the device first.  The reference's
+ * counterpart is the 100 s after which its tuner gives a run up (grid.py:125-133);
+ * here a wait that runs out ends the kernel with RDB_DEVICE_TIMEOUT in the
+ * status word and leaves the GPU usable.  Ranks of an allreduce may enter a call
+ * up to one budget apart before the early ones give up. */
+int rdb_set_wait_budget_ns(unsigned long long ns);
+
 /* Library version string and the SM architecture the kernels were built for. */
 const char *rdb_version(void);
 
@@ -67,6 +75,19 @@ const char *rdb_version(void);
  * rdb_skinny_gemm_fp8_hinted below. */
 int rdb_skinny_gemm_fp8(const uint8_t *A, const uint8_t *B, const float *scale_a, const float *scale_b,
                         uint16_t *D, int M, int N, int K, int ldb, void *stream);
+
+/* The same contraction for operands in HOST memory - what a caller that keeps
+ * its tensors on the host does end to end (the reference's drivers do the same
+ * steps around their launch: tensor_h2d, kernel, tensor_d2h of projects/
+ * common.cuh:50-60).  All five pointers are host pointers (pinned memory makes
+ * the copies asynchronous); A, B and the two scales are copied to device
+ * staging, the kernel runs, D is copied back, all on `stream`, and the call
+ * returns once D holds the result.  Exception to "nothing is allocated per
+ * call": the per-device staging buffers grow when a larger operand arrives
+ * and are kept until the process exits.  Returns RDB_DEVICE_TIMEOUT if the
+ * device status word holds a time-out when the result has arrived. */
+int rdb_skinny_gemm_fp8_host(const uint8_t *A, const uint8_t *B, const float *scale_a, const float *scale_b,
+                             uint16_t *D, int M, int N, int K, int ldb, void *stream);
 
 /* Same contraction with the reference's tuning arguments
  * (projects/skinny_gemm/skinny_gemm_caller.cu:20-43).  split_k (1..8, 0 =
@@ -104,6 +125,45 @@ int rdb_skinny_gemm_plan(int M, int N, int K, int sm_count, int *rows_per_tile, 
  * reference sizes its grid from a constant instead
  * (projects/skinny_gemm/core.cu:26, skinny_gemm_caller.cu:78). */
 int rdb_skinny_gemm_max_clusters(int M, int cluster_size, int smem_bytes);
+
+/* A list of independent skinny GEMMs in ONE persistent launch - what the
+ * reference's timed region is (BATCH back-to-back skinny_gemm_fastpath calls on
+ * different weight matrices, projects/skinny_gemm/bench.cu:51-60) and what a
+ * decode step issues per layer.  The weight matrices of all problems are
+ * streamed as one sequence split evenly over the SMs, so the per-launch
+ * start-up and drain of rdb_skinny_gemm_fp8 is paid once per list instead of
+ * once per matrix.  Every problem follows the rules of rdb_skinny_gemm_fp8
+ * (same return codes); count is 1..RDB_SKINNY_GROUP_MAX.  Results are
+ * deterministic (a fixed K-order sum per shape list) but, K being cut at
+ * different places, may differ from rdb_skinny_gemm_fp8's in the last bf16 bit.
+ *   - The problems must be independent: no D of the list may be an A or B of it.
+ *   - Tiles shared by several CTAs are reduced through a per-device workspace
+ *     (4.7 MiB, allocated on the first call): grouped calls on one device must
+ *     be ordered (same stream, or otherwise serialised), not concurrent. */
+#define RDB_SKINNY_GROUP_MAX 32
+typedef struct rdb_skinny_problem {
+    const uint8_t *A;        /* [M,K] e4m3, row-major */
+    const uint8_t *B;        /* [N,K] e4m3, K-contiguous, row pitch ldb */
+    const float *scale_a;    /* one fp32 each, on the device */
+    const float *scale_b;
+    uint16_t *D;             /* [M,N] bf16, overwritten */
+    int M, N, K, ldb;
+} rdb_skinny_problem;
+int rdb_skinny_gemm_fp8_grouped(const rdb_skinny_problem *problems, int count, void *stream);
+
+/* The work split of a grouped call on `ctas` CTAs (pure host arithmetic, no
+ * GPU): rows_per_unit[count] weight rows per streamed unit of each problem and
+ * range_begin[ctas + 1], the first unit of each CTA's contiguous range (units
+ * are numbered problem by problem, tile by tile, along K).  Either output may
+ * be NULL.  Counterpart of the tile arithmetic of projects/skinny_gemm/
+ * skinny_gemm_kernel.cu:44-69. */
+int rdb_skinny_gemm_grouped_plan(const rdb_skinny_problem *problems, int count, int ctas, int *rows_per_unit,
+                                 int *range_begin);
+
+/* Diagnostics: registers a device buffer of (SM count) x 4 uint64; while
+ * registered every grouped launch stores per CTA the %globaltimer at entry, at
+ * its first full stage, after its last MMA and at exit.  NULL switches it off. */
+int rdb_skinny_gemm_grouped_trace(unsigned long long *device_buffer);
 
 /* Diagnostics (the reference's counterpart is reading the saved ISA,
  * class_project.py:56-61): registers a device buffer of slots x ctas_per_slot
@@ -211,6 +271,17 @@ int rdb_ar_destroy(void *ctx);
  * algorithm then uses multimem.st (one store reaches all ranks).  NULL switches
  * back to per-peer stores.  Every rank must make the same choice. */
 int rdb_ar_set_multicast(void *ctx, void *multicast_workspace);
+/* Optional: result buffers that peers may write.  `buffers` holds `world`
+ * device pointers in rank order (the own one at index rank), each to `bytes`
+ * bytes that every rank can store into - e.g. allocations of
+ * rdb_ar_workspace_alloc shared through rdb_ar_ipc_export / _import, or a
+ * symmetric-memory allocation.  A two-shot call (algo 2, or 0 resolving to 2)
+ * whose `out` lies inside the own registered buffer then has every rank store
+ * its reduced shard straight into all ranks' buffers at that offset, and the
+ * copy out of the workspace disappears; every rank must pass the same offset.
+ * Same result bits.  NULL unregisters.  Like rdb_ar_result, the buffer must not
+ * be read by work queued after this rank's NEXT call. */
+int rdb_ar_register_buffers(void *ctx, void *const *buffers, size_t bytes);
 /* Diagnostics: registers a device buffer of 16 uint64.  While registered, each
  * rdb_ar_allreduce call stores %globaltimer stamps of its first CTA in words
  * 0-5 (entry, own pushes issued, all ranks' pushes arrived, own reduction and
@@ -218,7 +289,14 @@ int rdb_ar_set_multicast(void *ctx, void *multicast_workspace);
  * CTA in words 8-13.  NULL switches it off.  No reference counterpart. */
 int rdb_ar_set_trace(void *ctx, unsigned long long *device_buffer16);
 
-/* Collective: every rank calls it with the same n (a multiple of 128, at most
+/* Failure behaviour: every wait is bounded (rdb_set_wait_budget_ns).  A rank
+ * whose wait for its peers' encoded blocks runs out reports RDB_DEVICE_TIMEOUT
+ * in its status word and still publishes its "delivered" flag, marked failed,
+ * so that the others neither wait for it nor take its missing shard for
+ * delivered: they report RDB_DEVICE_TIMEOUT too and leave `out` unwritten.
+ * rdb_device_status() after a call tells whether `out` is valid.
+ *
+ * Collective: every rank calls it with the same n (a multiple of 128, at most
  * max_elems) and algo (0 automatic: one-shot up to 2^19 elements - up to 2^20
  * with two ranks - when out is given, else two-shot; 1 one-shot: every rank
  * receives and reduces everything, n <= 2^20; 2 two-shot: FP8 reduce-scatter
@@ -269,8 +347,11 @@ int rdb_debug_division_mismatches(const float *divisors, int count, unsigned lon
  * other allocating routine: the two barrier counters and a status word live in
  * a 256-byte array compiled into the library (each GPU that loads the library
  * holds it until the process exits).  The caller still passes D.
- *   - Limit: at most 1024 blocks and blocks x rounds <= 2^30; anything larger
- *     returns RDB_SIZE_ABOVE_LIMIT and prints the reason on stderr.
+ *   - Limit: at most 1024 blocks, blocks x rounds <= 2^30, and no more blocks
+ *     than the device can hold at once (the barrier needs the whole grid
+ *     resident: 148 SMs x the blocks of `threads` threads that fit one SM);
+ *     anything larger returns RDB_SIZE_ABOVE_LIMIT and prints the reason on
+ *     stderr, before anything is queued on the stream.
  *   - The first call on each device looks up the array's device address; make
  *     that first call before starting any stream capture.
  *   - All calls on one GPU share the array.  The counters are cleared (on
@@ -278,7 +359,8 @@ int rdb_debug_division_mismatches(const float *divisors, int count, unsigned lon
  *     previous one left behind; two calls whose kernels overlap on the GPU
  *     (different streams) race on the counters - serialise them.
  *   - A timed-out barrier is reported through rdb_noalloc_status(), not
- *     through rdb_device_status(). */
+ *     through rdb_device_status().  The word is sticky: it keeps a time-out
+ *     until rdb_noalloc_status() has returned it, also across later calls. */
 int rdb_globs_n_noalloc(uint32_t *D, int blocks, int threads, int rounds, void *stream);
 
 /* Synchronises the current device and returns (and clears) the status word of

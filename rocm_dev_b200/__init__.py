@@ -15,6 +15,8 @@ from .skinny_gemm import (  # noqa: F401
     skinny_gemm,
     skinny_gemm_fastpath,
     skinny_gemm_fp8,
+    skinny_gemm_fp8_grouped,
     skinny_gemm_fp8_host,
+    skinny_gemm_grouped_plan,
     skinny_gemm_fp8_tuned,
 )

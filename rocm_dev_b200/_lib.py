@@ -21,11 +21,16 @@ _SIGNATURES = {
     "rdb_status_string": (C.c_char_p, [i]),
     "rdb_device_status": (i, []),
     "rdb_version": (C.c_char_p, []),
+    "rdb_set_wait_budget_ns": (i, [C.c_ulonglong]),
     "rdb_skinny_gemm_fp8": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, vp]),
+    "rdb_skinny_gemm_fp8_host": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, vp]),
     "rdb_skinny_gemm_fp8_hinted": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, i, i, i, i, i, i, i, i, vp]),
     "rdb_skinny_gemm_plan": (i, [i, i, i, i, vp, vp, vp]),
     "rdb_skinny_gemm_max_clusters": (i, [i, i, i]),
     "rdb_skinny_gemm_trace": (i, [vp, i, i]),
+    "rdb_skinny_gemm_fp8_grouped": (i, [vp, i, vp]),
+    "rdb_skinny_gemm_grouped_plan": (i, [vp, i, i, vp, vp]),
+    "rdb_skinny_gemm_grouped_trace": (i, [vp]),
     "rdb_skinny_gemm_fp8_tuned": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, i, i, i, C.c_uint, vp]),
     "rdb_dense_gemm_fp8": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, vp]),
     "rdb_dense_gemm_fp8_tuned": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, i, vp]),
@@ -47,6 +52,7 @@ _SIGNATURES = {
     "rdb_ar_destroy": (i, [vp]),
     "rdb_ar_set_multicast": (i, [vp, vp]),
     "rdb_ar_set_trace": (i, [vp, vp]),
+    "rdb_ar_register_buffers": (i, [vp, C.POINTER(C.c_void_p), C.c_size_t]),
     "rdb_ar_allreduce": (i, [vp, vp, vp, C.c_size_t, i, vp]),
     "rdb_ar_result": (C.c_void_p, [vp]),
     "rdb_ar_begin_call": (i, [vp]),

@@ -39,8 +39,8 @@ def quantize_blocks128(x: torch.Tensor):
 
 
 class _Workspace:
-    def __init__(self, world: int, max_elems: int):
-        self.bytes = int(lib().rdb_ar_workspace_bytes(world, max_elems))
+    def __init__(self, world: int, max_elems: int, nbytes: int | None = None):
+        self.bytes = int(lib().rdb_ar_workspace_bytes(world, max_elems)) if nbytes is None else int(nbytes)
         if self.bytes == 0:
             raise ValueError("world must be 1..8 and max_elems positive")
         p = C.c_void_p()
@@ -91,6 +91,7 @@ class Fp8AllReduce:
         self.device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
         self.max_elems = int(max_elems)
         self.peers, self.ws, self.symm, self.multicast = [], None, None, False
+        self.reg_ws, self.reg_symm = None, None
         nbytes = int(lib().rdb_ar_workspace_bytes(self.world, self.max_elems))
         if nbytes == 0:
             raise ValueError("world must be 1..8 and max_elems positive")
@@ -146,7 +147,63 @@ class Fp8AllReduce:
         mc = int(getattr(hdl, "multicast_ptr", 0) or 0)
         return [int(p) for p in hdl.buffer_ptrs], mc
 
-    def all_reduce(self, x: torch.Tensor, out: torch.Tensor | None = None, algo: int = AUTO) -> torch.Tensor:
+    def new_result_buffer(self, nelems: int) -> torch.Tensor:
+        """Collective: a bf16 tensor of `nelems` elements that every rank can
+        store into, registered with the context (rdb_ar_register_buffers).  A
+        two-shot ``all_reduce(x, out=<this tensor or a leading slice of it>)``
+        then delivers the reduced shards straight into every rank's tensor -
+        no copy out of the workspace.  One registered buffer per object; a
+        second call replaces the first.  Its contents are valid until work
+        queued after this rank's next call."""
+        import torch.distributed as dist
+        nbytes = (int(nelems) * 2 + 255) // 256 * 256
+        with torch.cuda.device(self.device):
+            self._drop_result_buffer()
+            if self.backend == "symm":
+                import torch.distributed._symmetric_memory as symm_mem
+                grp = self.group if self.group is not None else dist.group.WORLD
+                buf = symm_mem.empty(nbytes, dtype=torch.uint8, device=self.device)
+                hdl = symm_mem.rendezvous(buf, grp)
+                self.reg_symm = (buf, hdl)
+                ptrs, own = [int(p) for p in hdl.buffer_ptrs], buf.data_ptr()
+            else:
+                self.reg_ws = _Workspace(self.world, 0, nbytes=nbytes)
+                handles = [None] * self.world
+                dist.all_gather_object(handles, self.reg_ws.handle(), group=self.group)
+                ptrs, self.reg_peers = [], []
+                for r, h in enumerate(handles):
+                    if r == self.rank:
+                        ptrs.append(self.reg_ws.ptr)
+                        continue
+                    p = C.c_void_p()
+                    check(lib().rdb_ar_ipc_import(h, C.byref(p)), "rdb_ar_ipc_import")
+                    self.reg_peers.append(p.value)
+                    ptrs.append(p.value)
+                own = self.reg_ws.ptr
+            arr = (C.c_void_p * self.world)(*ptrs)
+            check(lib().rdb_ar_register_buffers(self.ctx, arr, nbytes), "rdb_ar_register_buffers")
+            dist.barrier(group=self.group)
+            return torch.as_tensor(_DeviceView(own, int(nelems)), device=self.device).view(torch.bfloat16)
+
+    def _drop_result_buffer(self):
+        if self.reg_ws is None and self.reg_symm is None:
+            return
+        torch.cuda.synchronize(self.device)
+        if getattr(self, "ctx", None):
+            lib().rdb_ar_register_buffers(self.ctx, None, 0)
+        for p in getattr(self, "reg_peers", []):
+            lib().rdb_ar_ipc_close(p)
+        self.reg_peers = []
+        if self.reg_ws is not None:
+            self.reg_ws.free()
+        self.reg_ws, self.reg_symm = None, None
+
+    def all_reduce(self, x: torch.Tensor, out: torch.Tensor | None = None, algo: int = AUTO,
+                   check_status: bool = False) -> torch.Tensor:
+        """``check_status=True`` synchronises the device after the call and
+        raises if a bounded wait ran out (this rank's, or one a peer reported):
+        ``out`` is not valid then.  Without it the call is asynchronous and the
+        caller reads ``rdb_device_status()`` when it next synchronises."""
         assert x.is_cuda and x.dtype == torch.bfloat16 and x.is_contiguous()
         n = x.numel()
         if out is None:
@@ -155,6 +212,8 @@ class Fp8AllReduce:
         with torch.cuda.device(self.device):
             check(lib().rdb_ar_allreduce(self.ctx, x.data_ptr(), out.data_ptr(), n, algo,
                                          torch.cuda.current_stream(self.device).cuda_stream), "rdb_ar_allreduce")
+            if check_status:
+                check(lib().rdb_device_status(), "rdb_ar_allreduce (device status)")
         return out
 
     def all_reduce_in_workspace(self, x: torch.Tensor) -> torch.Tensor:
@@ -171,6 +230,7 @@ class Fp8AllReduce:
     def close(self):
         if getattr(self, "ctx", None):
             torch.cuda.synchronize(self.device)
+            self._drop_result_buffer()
             lib().rdb_ar_destroy(self.ctx)
             self.ctx = None
             for p in self.peers:
@@ -191,11 +251,25 @@ class LocalRanks:
             self.ws = [_Workspace(world, max_elems) for _ in range(world)]
             ptrs = [w.ptr for w in self.ws]
             self.ctx = [_create(r, world, ptrs, max_elems) for r in range(world)]
+        self.reg = []
 
-    def all_reduce(self, xs, algo: int = AUTO):
+    def new_result_buffers(self, nelems: int):
+        """One registered result buffer per emulated rank (see
+        Fp8AllReduce.new_result_buffer); returns the W bf16 tensors."""
+        nbytes = (int(nelems) * 2 + 255) // 256 * 256
+        with torch.cuda.device(self.device):
+            self.reg = [_Workspace(self.world, 0, nbytes=nbytes) for _ in range(self.world)]
+            arr = (C.c_void_p * self.world)(*[w.ptr for w in self.reg])
+            for c in self.ctx:
+                check(lib().rdb_ar_register_buffers(c, arr, nbytes), "rdb_ar_register_buffers")
+            return [torch.as_tensor(_DeviceView(w.ptr, int(nelems)), device=self.device).view(torch.bfloat16)
+                    for w in self.reg]
+
+    def all_reduce(self, xs, algo: int = AUTO, outs=None):
         """xs: list of W bf16 tensors (one per emulated rank) -> list of W results."""
         n = xs[0].numel()
-        outs = [torch.empty_like(x) for x in xs]
+        if outs is None:
+            outs = [torch.empty_like(x) for x in xs]
         stream = torch.cuda.current_stream(self.device).cuda_stream
         with torch.cuda.device(self.device):
             epochs = {int(lib().rdb_ar_begin_call(c)) for c in self.ctx}
@@ -211,6 +285,6 @@ class LocalRanks:
         torch.cuda.synchronize(self.device)
         for c in self.ctx:
             lib().rdb_ar_destroy(c)
-        for w in self.ws:
+        for w in self.ws + self.reg:
             w.free()
-        self.ctx, self.ws = [], []
+        self.ctx, self.ws, self.reg = [], [], []

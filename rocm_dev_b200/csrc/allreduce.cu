@@ -51,6 +51,8 @@
 #include "host_util.h"
 #include "ptx.cuh"
 
+RDB_DEFINE_WAIT_BUDGET_SETTER()
+
 namespace rdb {
 namespace ar {
 
@@ -66,7 +68,8 @@ struct Layout {
     size_t off_s;         // [2][W][slot_groups * 4] floats
     size_t off_gather;    // [max_elems] bf16; the FP8 all-gather uses it as [max_elems] codes + scales at gather_scale_off
     size_t gather_scale_off;   // relative to off_gather
-    size_t off_flags;     // [2 phases][2 epoch parities][kMaxWorld] uint32 epochs, then 4 block counters at word 64
+    size_t off_flags;     // [2 phases][2 epoch parities][kMaxWorld] uint32 flag words (epoch << 1 | failed), then 4 block
+                          // counters at word 64 and 4 "a block of this launch gave up" words at word 68
     size_t bytes;
 };
 
@@ -93,6 +96,8 @@ struct Ctx {
     Layout L;
     uint8_t* ws[kMaxWorld];
     uint8_t* mc;          // optional NVLS multicast alias of the workspace (same layout), else nullptr
+    uint8_t* reg[kMaxWorld];   // optional: every rank's registered result buffer (rank order), else nullptr
+    size_t reg_bytes;
     unsigned epoch;
     int push_order;       // 0 linear, 1 rotated by rank, 2 owner-interleaved (default)
     unsigned long long* trace;   // optional: 8 globaltimer stamps of the last fused call (diagnostics)
@@ -111,6 +116,8 @@ struct KParams {
     int push_order;
     const __nv_bfloat16* x;
     __nv_bfloat16* out;  // may be nullptr (two-shot: result stays in the gather area)
+    uint8_t* reg[kMaxWorld];   // direct delivery: every rank's registered result buffer, already offset to this call's
+                               // position; reg[0] == nullptr means the result travels through the gather area
     int* status;
     unsigned long long* trace;
 };
@@ -203,37 +210,47 @@ __device__ __forceinline__ uint4 regroup16(const uint2* q, int lane) {
 
 // Called by every block at the end of a producing phase: the last block of the
 // grid to get here (counted in a word of the own workspace, after a system-wide
-// fence) publishes `epoch` in word [which][my rank] of every rank's flag block.
-// Publishing at the end of the producer - not at the start of the consumer -
-// means a consumer launch never depends on a launch issued after it.
-__device__ __forceinline__ void publish_when_grid_done(const KParams& p, int which) {
+// fence) publishes this call's flag word - (epoch << 1) | failed - in word
+// [which][my rank] of every rank's flag block.  `failed` is set by any block
+// whose preceding wait gave up: the data this rank was to deliver is then
+// missing, and the low bit tells the peers so instead of letting them consume
+// a result that was never written.  Publishing at the end of the producer - not
+// at the start of the consumer - means a consumer launch never depends on a
+// launch issued after it.
+__device__ __forceinline__ void publish_when_grid_done(const KParams& p, int which, bool failed) {
     __syncthreads();
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
-        unsigned last = 0;
+        unsigned word = 0;
         if (lane == 0) {
+            unsigned* own = reinterpret_cast<unsigned*>(p.ws[p.rank] + p.L.off_flags);
+            unsigned* cnt = own + 64 + which * 2 + (p.epoch & 1u);   // two calls may be in flight
+            unsigned* bad = own + 68 + which * 2 + (p.epoch & 1u);
+            if (failed) atomicOr(bad, 1u);
             __threadfence_system();
-            unsigned* cnt = reinterpret_cast<unsigned*>(p.ws[p.rank] + p.L.off_flags) + 64 + which * 2 + (p.epoch & 1u);   // two calls may be in flight
             const unsigned old = atomicAdd(cnt, 1u);
             if (old == gridDim.x - 1) {
+                const unsigned any_failed = atomicExch(bad, 0u);
                 *cnt = 0;                      // ready for the next launch
                 __threadfence_system();
-                last = 1;
+                word = 0x80000000u | (any_failed & 1u);
             }
         }
-        last = __shfl_sync(0xffffffffu, last, 0);
+        word = __shfl_sync(0xffffffffu, word, 0);
         __syncwarp();
         // one lane per peer: the W release stores travel concurrently
-        if (last && lane < p.world) {
+        if (word && lane < p.world) {
             unsigned* f = reinterpret_cast<unsigned*>(p.ws[lane] + p.L.off_flags) + (which * 2 + (p.epoch & 1u)) * kMaxWorld + p.rank;
-            st_release_sys(f, p.epoch);
+            st_release_sys(f, (p.epoch << 1) | (word & 1u));
         }
     }
 }
 
-// Every block waits (bounded) until all ranks have published `epoch` in row
-// `which` of this rank's flag block; lane r of the first warp polls rank r's
-// word, so the W acquire loads overlap.  Returns false on timeout.
+// Every block waits (bounded) until all ranks have published this call's flag
+// in row `which` of this rank's flag block; lane r of the first warp polls rank
+// r's word, so the W acquire loads overlap.  Returns true when every rank
+// arrived and none of them reported a failure; otherwise the status word gets
+// RDB_DEVICE_TIMEOUT (the own wait ran out, or a peer's did and it said so).
 __device__ __forceinline__ bool wait_flags(const KParams& p, int which) {
     __shared__ int ok_s;
     if (threadIdx.x < 32) {
@@ -243,12 +260,13 @@ __device__ __forceinline__ bool wait_flags(const KParams& p, int which) {
         const unsigned* mine = reinterpret_cast<const unsigned*>(p.ws[p.rank] + p.L.off_flags) + (which * 2 + (p.epoch & 1u)) * kMaxWorld;
         bool ok = true;
         if (lane < p.world) {
-            const uint64_t t0 = globaltimer_ns();
-            unsigned spins = 0;
+            const uint64_t t0 = globaltimer_ns(), budget = wait_budget_ns();
+            unsigned spins = 0, v;
             // epochs only grow; a flag at or beyond this call's epoch means "arrived"
-            while (static_cast<int>(ld_acquire_sys(mine + lane) - p.epoch) < 0) {
-                if ((++spins & 0xFF) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) { ok = false; break; }
+            while (static_cast<int>(((v = ld_acquire_sys(mine + lane)) >> 1) - p.epoch) < 0) {
+                if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > budget) { ok = false; break; }
             }
+            if (ok && (v >> 1) == p.epoch && (v & 1u)) ok = false;   // that rank gave up before delivering
         }
         ok = __all_sync(0xffffffffu, ok);
         if (lane == 0) {
@@ -270,6 +288,41 @@ __device__ __forceinline__ void load_group(const __nv_bfloat16* x, size_t n, siz
     }
 }
 
+// Where work item `it` of the push phase goes: the group it encodes, the slot
+// position at the receiver and the receivers [first, last].  Returns false for
+// an item that does not exist (a shard one group shorter than the longest).
+struct PushItem {
+    size_t g, slot_g;
+    int first, last;
+};
+__device__ __forceinline__ bool push_item(const KParams& p, size_t it, size_t rot, PushItem& o) {
+    if (p.one_shot) {
+        o.g = o.slot_g = it;
+        o.first = 0;
+        o.last = p.world - 1;
+        return true;
+    }
+    if (p.push_order == 2) {
+        int owner = static_cast<int>(it % p.world) + p.rank + 1;
+        while (owner >= p.world) owner -= p.world;
+        o.slot_g = it / p.world;
+        const size_t b = group_begin(owner, p.groups, p.world);
+        if (b + o.slot_g >= group_begin(owner + 1, p.groups, p.world)) return false;   // this owner's shard is one group shorter
+        o.g = b + o.slot_g;
+        o.first = o.last = owner;
+        return true;
+    }
+    size_t g = it + rot;
+    if (g >= p.groups) g -= p.groups;
+    int owner = static_cast<int>((g * p.world + p.world - 1) / p.groups);   // owner: largest o with begin(o) <= g
+    while (owner + 1 < p.world && group_begin(owner + 1, p.groups, p.world) <= g) owner++;
+    while (owner > 0 && group_begin(owner, p.groups, p.world) > g) owner--;
+    o.g = g;
+    o.first = o.last = owner;
+    o.slot_g = g - group_begin(owner, p.groups, p.world);
+    return true;
+}
+
 __device__ __forceinline__ void push_body(const KParams& p) {
     const int lane = threadIdx.x & 31;
     const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
@@ -283,54 +336,45 @@ __device__ __forceinline__ void push_body(const KParams& p) {
     const size_t shard_max = (p.groups + p.world - 1) / p.world;
     const size_t items = (p.one_shot || p.push_order != 2) ? p.groups : shard_max * p.world;
     const size_t rot = (!p.one_shot && p.push_order == 1) ? group_begin((p.rank + 1) % p.world, p.groups, p.world) : 0;
+    // The loads of the next item are issued before the current one is encoded:
+    // the encoder is bound by load latency (two 16-byte loads per lane and item),
+    // and this keeps four of them in flight per lane.
+    PushItem cur, nxt;
+    uint4 in[2], in_next[2];
+    bool have = warp < items && push_item(p, warp, rot, cur);
+    if (have) load_group(p.x, p.n, cur.g, lane, in);
     for (size_t it = warp; it < items; it += nwarps) {
-        size_t g, slot_g;
-        int first, last;
-        if (p.one_shot) {
-            g = slot_g = it;
-            first = 0;
-            last = p.world - 1;
-        } else if (p.push_order == 2) {
-            int o = static_cast<int>(it % p.world) + p.rank + 1;
-            while (o >= p.world) o -= p.world;
-            slot_g = it / p.world;
-            const size_t b = group_begin(o, p.groups, p.world);
-            if (b + slot_g >= group_begin(o + 1, p.groups, p.world)) continue;   // this owner's shard is one group shorter
-            g = b + slot_g;
-            first = last = o;
-        } else {
-            g = it + rot;
-            if (g >= p.groups) g -= p.groups;
-            int o = static_cast<int>((g * p.world + p.world - 1) / p.groups);   // owner: largest o with begin(o) <= g
-            while (o + 1 < p.world && group_begin(o + 1, p.groups, p.world) <= g) o++;
-            while (o > 0 && group_begin(o, p.groups, p.world) > g) o--;
-            first = last = o;
-            slot_g = g - group_begin(o, p.groups, p.world);
-        }
-        uint4 in[2];
-        load_group(p.x, p.n, g, lane, in);
-        uint2 q[2];
-        float s[2];
+        const size_t it_next = it + nwarps;
+        const bool have_next = it_next < items && push_item(p, it_next, rot, nxt);
+        if (have_next) load_group(p.x, p.n, nxt.g, lane, in_next);
+        if (have) {
+            uint2 q[2];
+            float s[2];
 #pragma unroll
-        for (int h = 0; h < 2; h++) q[h] = encode8(in[h], s[h]);
-        // the four block scales of the group: (half 0: lanes 0, 16), (half 1: lanes 0, 16)
-        const float s1 = __shfl_sync(0xffffffffu, s[0], 16), s3 = __shfl_sync(0xffffffffu, s[1], 16);
-        const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + p.rank) * p.L.slot_groups + slot_g;
-        const uint4 q16 = regroup16(q, lane);
-        for (int peer = first; peer <= last; peer++) {
-            uint8_t* base = p.ws[peer];
-            reinterpret_cast<uint4*>(base + p.L.off_q + slot * kGroup)[lane] = q16;
-            if (lane == 0) {
-                float4* ds = reinterpret_cast<float4*>(base + p.L.off_s) + slot;
-                *ds = make_float4(s[0], s1, s[1], s3);
+            for (int h = 0; h < 2; h++) q[h] = encode8(in[h], s[h]);
+            // the four block scales of the group: (half 0: lanes 0, 16), (half 1: lanes 0, 16)
+            const float s1 = __shfl_sync(0xffffffffu, s[0], 16), s3 = __shfl_sync(0xffffffffu, s[1], 16);
+            const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + p.rank) * p.L.slot_groups + cur.slot_g;
+            const uint4 q16 = regroup16(q, lane);
+            for (int peer = cur.first; peer <= cur.last; peer++) {
+                uint8_t* base = p.ws[peer];
+                reinterpret_cast<uint4*>(base + p.L.off_q + slot * kGroup)[lane] = q16;
+                if (lane == 0) {
+                    float4* ds = reinterpret_cast<float4*>(base + p.L.off_s) + slot;
+                    *ds = make_float4(s[0], s1, s[1], s3);
+                }
             }
         }
+        have = have_next;
+        cur = nxt;
+        in[0] = in_next[0];
+        in[1] = in_next[1];
     }
 }
 
 __global__ void __launch_bounds__(kThreads) ar_push_kernel(const KParams p) {
     push_body(p);
-    publish_when_grid_done(p, 0);
+    publish_when_grid_done(p, 0, false);
 }
 
 // ------------------------------------------------------------------ phase 2
@@ -399,6 +443,13 @@ __device__ __forceinline__ void reduce_body(const KParams& p, bool arrived) {
             if (e0 >= p.n) continue;
             if (p.one_shot) {
                 *reinterpret_cast<uint4*>(p.out + e0) = val[h];
+            } else if (p.reg[0]) {
+                // the ranks registered their result buffers: deliver straight into them
+                for (int i = 0; i < p.world; i++) {
+                    int peer = p.rank + 1 + i;
+                    if (peer >= p.world) peer -= p.world;
+                    *reinterpret_cast<uint4*>(p.reg[peer] + e0 * 2) = val[h];
+                }
             } else if (p.mc) {
                 multimem_st_v4(p.mc + p.L.off_gather + e0 * 2, val[h]);
             } else {
@@ -413,13 +464,16 @@ __device__ __forceinline__ void reduce_body(const KParams& p, bool arrived) {
 }
 
 __global__ void __launch_bounds__(kThreads) ar_reduce_kernel(const KParams p) {
-    reduce_body(p, wait_flags(p, 0));
-    if (!p.one_shot) publish_when_grid_done(p, 1);   // also after a timeout, so that peers are not left waiting
+    const bool arrived = wait_flags(p, 0);
+    reduce_body(p, arrived);
+    // also after a timeout, so that peers are not left waiting - with the failure bit set, so that
+    // they do not take the missing shard for delivered
+    if (!p.one_shot) publish_when_grid_done(p, 1, !arrived);
 }
 
 // ------------------------------------------------------------------ phase 3
 __device__ __forceinline__ void copy_out_body(const KParams& p) {
-    if (p.out == nullptr) return;
+    if (p.out == nullptr || (p.reg[0] != nullptr && !p.fp8_gather)) return;   // nothing to copy: left in place, or delivered directly
     if (p.fp8_gather) {
         // decode: out = bf16(fp32(code) * block scale), 8 elements per thread
         const uint8_t* gq = p.ws[p.rank] + p.L.off_gather;
@@ -458,8 +512,10 @@ __global__ void __launch_bounds__(kThreads) ar_gather_kernel(const KParams p) {
 // finish publishes this rank's flag, every CTA then waits for all ranks' flags
 // (its own included, which covers the pushes of its sibling CTAs), reduces, and
 // - two-shot - repeats the publish / wait step before copying the result out.
-// All CTAs must be resident together (the grid is capped accordingly), because
-// early CTAs wait for the last one.  Not usable when several ranks share one
+// All CTAs must be resident together, because early CTAs wait for the last one:
+// the grid is capped to what the occupancy calculator reports and the launch is
+// a cooperative one, so the runtime refuses a grid that cannot be co-resident
+// instead of letting part of it wait for blocks that cannot start.  Not usable when several ranks share one
 // GPU: that case uses the three separate launches above.
 // Diagnostics: block 0 and the last block stamp %globaltimer after each step.
 __device__ __forceinline__ void stamp(const KParams& p, int slot) {
@@ -473,13 +529,13 @@ __global__ void __launch_bounds__(kThreads, kBlocksPerSm) ar_fused_kernel(const 
     stamp(p, 0);
     push_body(p);
     stamp(p, 1);
-    publish_when_grid_done(p, 0);
+    publish_when_grid_done(p, 0, false);
     const bool arrived = wait_flags(p, 0);
     stamp(p, 2);
     reduce_body(p, arrived);
     stamp(p, 3);
     if (p.one_shot) return;
-    publish_when_grid_done(p, 1);
+    publish_when_grid_done(p, 1, !arrived);
     const bool gathered = wait_flags(p, 1);
     stamp(p, 4);
     if (gathered) copy_out_body(p);
@@ -581,8 +637,23 @@ static int run_phase(Ctx* c, int phase, const uint16_t* x, uint16_t* out, size_t
     p.out = reinterpret_cast<__nv_bfloat16*>(out);
     p.status = info->status_dev;
     p.trace = phase == 0 ? c->trace : nullptr;
+    // Direct delivery: `out` lies inside this rank's registered buffer, so the reduced shard is stored into
+    // every rank's registered buffer at the same offset and nothing passes through the gather area.
+    for (int i = 0; i < kMaxWorld; i++) p.reg[i] = nullptr;
+    if (algo == 2 && out && c->reg[c->rank]) {
+        const uintptr_t lo = reinterpret_cast<uintptr_t>(c->reg[c->rank]), o = reinterpret_cast<uintptr_t>(out);
+        if (o >= lo && o + n * 2 <= lo + c->reg_bytes)
+            for (int i = 0; i < c->world; i++) p.reg[i] = c->reg[i] + (o - lo);
+    }
     if (phase == 0) {
-        ar_fused_kernel<<<grid_for(p.groups, info->sm_count, fused_blocks_per_sm()), kThreads, 0, stream>>>(p);
+        void* args[] = {&p};
+        const int grid = grid_for(p.groups, info->sm_count, fused_blocks_per_sm());
+        if (cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ar_fused_kernel), dim3(grid), dim3(kThreads), args, 0, stream) !=
+            cudaSuccess) {
+            cudaGetLastError();
+            return RDB_CUDA_ERROR;
+        }
+        return RDB_SUCCESS;
     } else if (phase == 1) {
         ar_push_kernel<<<grid_for(p.groups, info->sm_count), kThreads, 0, stream>>>(p);
     } else if (phase == 2) {
@@ -654,8 +725,18 @@ int rdb_ar_create(int rank, int world, void* const* workspaces, size_t max_elems
     c->L = rdb::ar::make_layout(world, max_elems);
     for (int i = 0; i < rdb::ar::kMaxWorld; i++) c->ws[i] = i < world ? static_cast<uint8_t*>(workspaces[i]) : nullptr;
     c->mc = nullptr;
+    for (int i = 0; i < rdb::ar::kMaxWorld; i++) c->reg[i] = nullptr;
+    c->reg_bytes = 0;
     c->epoch = 0;
     c->trace = nullptr;
+    // The epoch restarts at zero, so flag words left by an earlier context over the same workspace must
+    // go: this rank's flag block is cleared here.  Creation is a collective set-up step - no rank may
+    // start a call before every rank's rdb_ar_create has returned.
+    if (cudaMemset(c->ws[rank] + c->L.off_flags, 0, 1024) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+        cudaGetLastError();
+        delete c;
+        return RDB_CUDA_ERROR;
+    }
     // tuning override for A/B measurements: RDB_AR_PUSH_ORDER = 0 (linear), 1 (rotated), 2 (interleaved, default)
     const char* po = getenv("RDB_AR_PUSH_ORDER");
     c->push_order = (po && po[0] >= '0' && po[0] <= '2' && !po[1]) ? po[0] - '0' : 2;
@@ -668,6 +749,22 @@ int rdb_ar_set_multicast(void* ctx, void* multicast_workspace) {
     if (!c) return RDB_INVALID_CONFIG;
     if (multicast_workspace && !rdb::aligned16(multicast_workspace)) return RDB_BAD_ALIGNMENT;
     c->mc = static_cast<uint8_t*>(multicast_workspace);
+    return RDB_SUCCESS;
+}
+
+int rdb_ar_register_buffers(void* ctx, void* const* buffers, size_t bytes) {
+    rdb::ar::Ctx* c = static_cast<rdb::ar::Ctx*>(ctx);
+    if (!c) return RDB_INVALID_CONFIG;
+    if (!buffers) {
+        for (int i = 0; i < rdb::ar::kMaxWorld; i++) c->reg[i] = nullptr;
+        c->reg_bytes = 0;
+        return RDB_SUCCESS;
+    }
+    if (bytes == 0) return RDB_BAD_SHAPE;
+    for (int i = 0; i < c->world; i++)
+        if (!buffers[i] || !rdb::aligned16(buffers[i])) return RDB_BAD_ALIGNMENT;
+    for (int i = 0; i < c->world; i++) c->reg[i] = static_cast<uint8_t*>(buffers[i]);
+    c->reg_bytes = bytes;
     return RDB_SUCCESS;
 }
 
@@ -692,7 +789,9 @@ int rdb_ar_allreduce(void* ctx, const uint16_t* x, uint16_t* out, size_t n, int 
     // chunk i+1 over the all-gather of chunk i) was measured slower than one
     // call (187 vs 157 us at 64 MiB on two GPUs): not done.
     const unsigned epoch = ++c->epoch;
-    return run_phase(c, 0, x, out, n, algo, epoch, static_cast<cudaStream_t>(stream));   // 0 = all phases in one launch
+    r = run_phase(c, 0, x, out, n, algo, epoch, static_cast<cudaStream_t>(stream));   // 0 = all phases in one launch
+    if (r != RDB_SUCCESS) c->epoch--;    // nothing was launched: the ranks' epochs stay in step
+    return r;
 }
 
 int rdb_ar_begin_call(void* ctx) {

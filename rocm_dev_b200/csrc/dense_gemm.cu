@@ -25,6 +25,8 @@
 #include "host_util.h"
 #include "ptx.cuh"
 
+RDB_DEFINE_WAIT_BUDGET_SETTER()
+
 namespace rdb {
 namespace dense {
 
@@ -66,11 +68,12 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
 }
 
 // Epilogue store of 32 consecutive columns of one output row (scaled; bf16 or fp32).
+// vec8: 16-byte stores are safe (aligned D, row length a multiple of 16 bytes).
 __device__ __forceinline__ void store_row32(const Params& p, const float* v, float sc, int row, int col, bool vec8) {
     if (row >= p.M || col >= p.N) return;
     if (p.out_f32) {
         float* out = reinterpret_cast<float*>(p.D) + static_cast<size_t>(row) * p.N + col;
-        if (p.N % 4 == 0 && col + 31 < p.N) {
+        if (vec8 && col + 31 < p.N) {
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
                 *reinterpret_cast<float4*>(out + j) = make_float4(v[j] * sc, v[j + 1] * sc, v[j + 2] * sc, v[j + 3] * sc);
@@ -196,7 +199,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
         const int quad = warp & 3;
         float sc = 1.0f;
         if (p.scale_a) sc = __ldg(p.scale_a) * __ldg(p.scale_b);
-        const bool vec8 = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
+        // 16-byte stores need a 16-byte aligned D and rows that keep that alignment (8 bf16 or 4 fp32)
+        const bool vec8 = (p.N % (p.out_f32 ? 4 : 8) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
         int t = 0;
         bool live = true;
         for (int tile = blockIdx.x; tile < num_tiles && live; tile += gridDim.x, t++) {
@@ -379,7 +383,8 @@ dense_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
         const int quad = warp & 3;
         float sc = 1.0f;
         if (p.scale_a) sc = __ldg(p.scale_a) * __ldg(p.scale_b);
-        const bool vec8 = (p.N % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
+        // 16-byte stores need a 16-byte aligned D and rows that keep that alignment (8 bf16 or 4 fp32)
+        const bool vec8 = (p.N % (p.out_f32 ? 4 : 8) == 0) && ((reinterpret_cast<uintptr_t>(p.D) & 15u) == 0);
         const uint32_t acc_empty_even0 = mapa_smem(acc_empty0, 0);
         int t = 0;
         for (int tile = pair_id; tile < num_tiles; tile += num_pairs, t++) {

@@ -13,6 +13,11 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 EncodeTiledFn g_encode = nullptr;
 
+// Filled during static initialisation of the kernel source files: plain arrays
+// (zero-initialised before any constructor runs), so the order does not matter.
+WaitBudgetSetter g_budget_setters[16];
+int g_num_budget_setters = 0;
+
 EncodeTiledFn encode_fn() {
     if (g_encode) return g_encode;
     std::lock_guard<std::mutex> lk(g_mu);
@@ -26,6 +31,10 @@ EncodeTiledFn encode_fn() {
     return g_encode;
 }
 }  // namespace
+
+void register_wait_budget_setter(WaitBudgetSetter fn) {
+    if (g_num_budget_setters < 16) g_budget_setters[g_num_budget_setters++] = fn;
+}
 
 DeviceInfo* device_info(int* err) {
     int dev = 0;
@@ -108,6 +117,16 @@ int rdb_device_status(void) {
     const int s = *reinterpret_cast<volatile int*>(d->status_host);
     *reinterpret_cast<volatile int*>(d->status_host) = 0;
     return s;
+}
+
+int rdb_set_wait_budget_ns(unsigned long long ns) {
+    if (ns == 0) return RDB_BAD_SHAPE;
+    if (cudaDeviceSynchronize() != cudaSuccess) return RDB_CUDA_ERROR;   // no kernel reads the word while it changes
+    for (int i = 0; i < rdb::g_num_budget_setters; i++) {
+        const int r = rdb::g_budget_setters[i](ns);
+        if (r != RDB_SUCCESS) return r;
+    }
+    return RDB_SUCCESS;
 }
 
 const char* rdb_version(void) { return "rocm_dev_b200 0.1 (sm_100a)"; }

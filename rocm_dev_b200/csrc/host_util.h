@@ -40,4 +40,22 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, 
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// The device word holding the wait budget exists once per translation unit
+// (ptx.cuh).  Each kernel source file names RDB_DEFINE_WAIT_BUDGET_SETTER once
+// at namespace scope: it registers a function that writes that unit's copy on
+// the current device, and rdb_set_wait_budget_ns calls all of them.
+typedef int (*WaitBudgetSetter)(unsigned long long ns);
+void register_wait_budget_setter(WaitBudgetSetter fn);
+
+#define RDB_DEFINE_WAIT_BUDGET_SETTER()                                                                        \
+    namespace {                                                                                                \
+    int set_wait_budget_of_this_unit(unsigned long long ns) {                                                  \
+        return cudaMemcpyToSymbol(rdb::d_wait_budget_ns, &ns, sizeof(ns)) == cudaSuccess ? RDB_SUCCESS         \
+                                                                                        : RDB_CUDA_ERROR;      \
+    }                                                                                                          \
+    struct WaitBudgetRegistration {                                                                            \
+        WaitBudgetRegistration() { rdb::register_wait_budget_setter(&set_wait_budget_of_this_unit); }          \
+    } wait_budget_registration;                                                                                \
+    }
+
 }  // namespace rdb

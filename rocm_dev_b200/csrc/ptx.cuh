@@ -59,8 +59,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     return ok != 0;
 }
 
-// Wait budget of every bounded wait, in nanoseconds of %globaltimer.
-constexpr uint64_t kWaitBudgetNs = 1000ull * 1000ull * 1000ull;
+// Wait budget of every bounded wait, in nanoseconds of %globaltimer (default
+// one second).  The library is built without relocatable device code, so every
+// translation unit holds its own copy of this word; RDB_DEFINE_WAIT_BUDGET_SETTER
+// (host_util.h) registers a setter per unit and rdb_set_wait_budget_ns updates
+// them all on the current device.  It is read only on the slow path of a wait.
+static __device__ unsigned long long d_wait_budget_ns = 1000ull * 1000ull * 1000ull;
+__device__ __forceinline__ uint64_t wait_budget_ns() {
+    return *reinterpret_cast<volatile unsigned long long*>(&d_wait_budget_ns);
+}
 
 // Bounded phase wait.  Returns false when the budget ran out.  %globaltimer is
 // slow to read (a read per wait capped a TMA pipeline at one box per ~260 ns),
@@ -71,10 +78,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
 #pragma unroll 1
     for (int i = 0; i < 2048; i++)
         if (mbar_try_wait(bar, parity)) return true;
-    const uint64_t t0 = globaltimer_ns();
+    const uint64_t t0 = globaltimer_ns(), budget = wait_budget_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
-        if ((++spins & 0x3FF) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) return false;
+        if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > budget) return false;
     }
     return true;
 }
@@ -242,7 +249,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity)
             : "memory");
         if (ok) return true;
         if (++spins == 2048) t0 = globaltimer_ns();
-        if (spins > 2048 && (spins & 0x3FF) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) return false;
+        if (spins > 2048 && (spins & 0x3F) == 0 && globaltimer_ns() - t0 > wait_budget_ns()) return false;
     }
 }
 

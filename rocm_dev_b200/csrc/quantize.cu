@@ -16,6 +16,8 @@
 #include "host_util.h"
 #include "sync.cuh"
 
+RDB_DEFINE_WAIT_BUDGET_SETTER()
+
 namespace rdb {
 namespace quant {
 

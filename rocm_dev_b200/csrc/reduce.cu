@@ -22,6 +22,8 @@
 #include "host_util.h"
 #include "sync.cuh"
 
+RDB_DEFINE_WAIT_BUDGET_SETTER()
+
 namespace rdb {
 namespace reduce {
 
@@ -113,7 +115,25 @@ int launch_globs(unsigned* D, unsigned* words, int blocks, int threads, int roun
     void* args[] = {&D, &words, &rounds, &status};
     const cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(globs_kernel), dim3(blocks), dim3(threads),
                                                       args, 0, stream);
-    return e == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
+    if (e != cudaSuccess) {
+        cudaGetLastError();      // do not leave the error for the next launch's check to trip over
+        return RDB_CUDA_ERROR;
+    }
+    return RDB_SUCCESS;
+}
+
+// Blocks of `threads` threads of the probe kernel the current device can hold at
+// once (a cooperative launch of more is refused); 0 when the query fails.
+// Queries only - nothing is allocated.
+static int globs_resident_blocks(int threads) {
+    int dev = 0, sms = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, globs_kernel, threads, 0) != cudaSuccess) {
+        cudaGetLastError();
+        return 0;
+    }
+    return sms * per_sm;
 }
 
 // ------------------------------------------------ allocation-free variant
@@ -198,6 +218,14 @@ int rdb_globs_n_noalloc(uint32_t* D, int blocks, int threads, int rounds, void* 
                 "rdb_globs_n_noalloc: %d blocks x %d rounds is beyond what the built-in scratch supports "
                 "(at most %d blocks and %lld barrier arrivals per launch)\n",
                 blocks, rounds, kNoAllocMaxBlocks, kNoAllocMaxArrivals);
+        return RDB_SIZE_ABOVE_LIMIT;
+    }
+    const int resident = globs_resident_blocks(threads);
+    if (resident > 0 && blocks > resident) {
+        fprintf(stderr,
+                "rdb_globs_n_noalloc: %d blocks of %d threads cannot be resident together on this device "
+                "(at most %d): the barrier needs the whole grid on the GPU at once\n",
+                blocks, threads, resident);
         return RDB_SIZE_ABOVE_LIMIT;
     }
     int err = 0;

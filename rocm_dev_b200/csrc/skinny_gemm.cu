@@ -33,6 +33,8 @@
 #include "host_util.h"
 #include "ptx.cuh"
 
+RDB_DEFINE_WAIT_BUDGET_SETTER()
+
 namespace rdb {
 namespace skinny {
 
@@ -529,6 +531,62 @@ static int run(const uint8_t* A, const uint8_t* B, const float* sa, const float*
     return launch<32>(tmW, tmA, prm, pl, pdl, stream);
 }
 
+// Device staging of the host-buffer entry: one set of buffers per device, grown
+// on demand and kept until the process exits.
+struct HostStaging {
+    uint8_t* a = nullptr;
+    uint8_t* b = nullptr;
+    uint16_t* d = nullptr;
+    float* scales = nullptr;
+    size_t a_cap = 0, b_cap = 0, d_cap = 0;
+};
+
+template <class T>
+static bool grow(T*& ptr, size_t& cap, size_t need) {
+    if (need <= cap) return true;
+    if (ptr && cudaFree(ptr) != cudaSuccess) return false;
+    ptr = nullptr;
+    cap = 0;
+    if (cudaMalloc(reinterpret_cast<void**>(&ptr), need) != cudaSuccess) { cudaGetLastError(); return false; }
+    cap = need;
+    return true;
+}
+
+static int run_host(const uint8_t* A, const uint8_t* B, const float* sa, const float* sb, uint16_t* D, int M, int N, int K,
+                    int ldb, cudaStream_t stream) {
+    if (!A || !B || !sa || !sb || !D) return RDB_INVALID_CONFIG;
+    if (M < 1 || N < 1 || K < 1 || ldb < K) return RDB_BAD_SHAPE;
+    static HostStaging staging[kMaxDevices];
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return RDB_CUDA_ERROR;
+    std::lock_guard<std::mutex> lk(mu);       // one host-buffer call per process at a time: they share the staging
+    HostStaging& st = staging[dev];
+    const size_t a_bytes = static_cast<size_t>(M) * K, b_bytes = static_cast<size_t>(N) * K;
+    const size_t d_bytes = static_cast<size_t>(M) * N * sizeof(uint16_t);
+    size_t sc_cap = st.scales ? 8 : 0;
+    if (!grow(st.a, st.a_cap, a_bytes) || !grow(st.b, st.b_cap, b_bytes) || !grow(st.d, st.d_cap, d_bytes) ||
+        !grow(st.scales, sc_cap, 8))
+        return RDB_CUDA_ERROR;
+    bool ok = cudaMemcpyAsync(st.a, A, a_bytes, cudaMemcpyHostToDevice, stream) == cudaSuccess;
+    // the weights land K-contiguous with pitch K whatever the host pitch was
+    ok = ok && cudaMemcpy2DAsync(st.b, K, B, ldb, K, N, cudaMemcpyHostToDevice, stream) == cudaSuccess;
+    ok = ok && cudaMemcpyAsync(st.scales, sa, sizeof(float), cudaMemcpyHostToDevice, stream) == cudaSuccess;
+    ok = ok && cudaMemcpyAsync(st.scales + 1, sb, sizeof(float), cudaMemcpyHostToDevice, stream) == cudaSuccess;
+    if (!ok) { cudaGetLastError(); return RDB_CUDA_ERROR; }
+    const int r = run(st.a, st.b, st.scales, st.scales + 1, st.d, M, N, K, K, 0, 0, 0, 0, stream);
+    if (r != RDB_SUCCESS) return r;
+    if (cudaMemcpyAsync(D, st.d, d_bytes, cudaMemcpyDeviceToHost, stream) != cudaSuccess ||
+        cudaStreamSynchronize(stream) != cudaSuccess) {
+        cudaGetLastError();
+        return RDB_CUDA_ERROR;
+    }
+    int err = 0;
+    DeviceInfo* info = device_info(&err);
+    if (info && *reinterpret_cast<volatile int*>(info->status_host) == RDB_DEVICE_TIMEOUT) return RDB_DEVICE_TIMEOUT;
+    return RDB_SUCCESS;
+}
+
 }  // namespace skinny
 }  // namespace rdb
 
@@ -537,6 +595,11 @@ extern "C" {
 int rdb_skinny_gemm_fp8(const uint8_t* A, const uint8_t* B, const float* scale_a, const float* scale_b, uint16_t* D,
                         int M, int N, int K, int ldb, void* stream) {
     return rdb::skinny::run(A, B, scale_a, scale_b, D, M, N, K, ldb, 0, 0, 0, 0, static_cast<cudaStream_t>(stream));
+}
+
+int rdb_skinny_gemm_fp8_host(const uint8_t* A, const uint8_t* B, const float* scale_a, const float* scale_b, uint16_t* D,
+                             int M, int N, int K, int ldb, void* stream) {
+    return rdb::skinny::run_host(A, B, scale_a, scale_b, D, M, N, K, ldb, static_cast<cudaStream_t>(stream));
 }
 
 int rdb_skinny_gemm_fp8_hinted(const uint8_t* A, const uint8_t* B, const float* scale_a, const float* scale_b,

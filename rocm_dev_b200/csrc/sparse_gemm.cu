@@ -25,6 +25,8 @@
 #include "host_util.h"
 #include "ptx.cuh"
 
+RDB_DEFINE_WAIT_BUDGET_SETTER()
+
 namespace rdb {
 namespace sparse {
 

@@ -32,10 +32,10 @@ __device__ __forceinline__ bool grid_barrier(unsigned* words, unsigned nblocks) 
         const unsigned target = old - old % nblocks + nblocks;
         bool ok = true;
         if (ld_acquire_gpu(words) < target) {
-            const uint64_t t0 = globaltimer_ns();
+            const uint64_t t0 = globaltimer_ns(), budget = wait_budget_ns();
             unsigned spins = 0;
             while (ld_acquire_gpu(words) < target) {
-                if ((++spins & 0x3FF) == 0 && globaltimer_ns() - t0 > kWaitBudgetNs) { ok = false; break; }
+                if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > budget) { ok = false; break; }
             }
         }
         ok_s = ok ? 1 : 0;

@@ -14,6 +14,7 @@ reference-named wrappers pass 1).
 """
 from __future__ import annotations
 
+import ctypes as C
 import enum
 
 import torch
@@ -95,6 +96,50 @@ def skinny_gemm_fp8_tuned(A, B, scale_a, scale_b, out, rows_per_tile=0, split_k=
                                                    stages, flags, _stream_ptr(A.device)))
 
 
+GROUP_MAX = 32
+
+
+class SkinnyProblem(C.Structure):
+    """``rdb_skinny_problem`` of include/rocm_dev_b200.h."""
+    _fields_ = [("A", C.c_void_p), ("B", C.c_void_p), ("scale_a", C.c_void_p), ("scale_b", C.c_void_p),
+                ("D", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int), ("ldb", C.c_int)]
+
+
+def _problem_array(problems):
+    arr = (SkinnyProblem * len(problems))()
+    for i, (A, B, sa, sb, D) in enumerate(problems):
+        A, B = _u8(A), _u8(B)
+        M, K = A.shape
+        arr[i] = SkinnyProblem(A.data_ptr(), B.data_ptr(), sa.data_ptr(), sb.data_ptr(), D.data_ptr(), M, B.shape[0], K,
+                               B.stride(0))
+    return arr
+
+
+def skinny_gemm_fp8_grouped(problems) -> int:
+    """A list of independent skinny GEMMs in one persistent launch
+    (rdb_skinny_gemm_fp8_grouped) - the shape of the reference's timed region,
+    BATCH back-to-back ``skinny_gemm_fastpath`` calls on different weights
+    (projects/skinny_gemm/bench.cu:51-60).  ``problems``: up to 32 tuples
+    ``(A, B, scale_a, scale_b, D)`` of device tensors with the meaning of
+    ``skinny_gemm_fp8``.  Returns the status code."""
+    dev = problems[0][0].device
+    arr = _problem_array(problems)
+    with torch.cuda.device(dev):
+        return int(lib().rdb_skinny_gemm_fp8_grouped(arr, len(problems), _stream_ptr(dev)))
+
+
+def skinny_gemm_grouped_plan(shapes, ctas: int = 148):
+    """Work split of a grouped call for ``shapes`` = [(M, N, K), ...]: (rows
+    per unit of each problem, first unit of each CTA's range).  No GPU needed."""
+    arr = (SkinnyProblem * len(shapes))()
+    for i, (M, N, K) in enumerate(shapes):
+        arr[i] = SkinnyProblem(None, None, None, None, None, M, N, K, K)
+    rows = (C.c_int * len(shapes))()
+    ranges = (C.c_int * (ctas + 1))()
+    check(lib().rdb_skinny_gemm_grouped_plan(arr, len(shapes), ctas, rows, ranges), "rdb_skinny_gemm_grouped_plan")
+    return list(rows), list(ranges)
+
+
 def skinny_gemm_fastpath(A, B, D, scale_tensor, m: int, n: int, k: int) -> int:
     """Reference-named launcher: returns the status code instead of raising.
 
@@ -138,39 +183,21 @@ class HFRK_skinny_gemm:
                            consumers, b_lanes, qsize, op_m, ops)
 
 
-class _HostStaging:
-    """Device buffers reused by the host-buffer entry (allocated once per shape)."""
-
-    def __init__(self):
-        self.bufs: dict[tuple, torch.Tensor] = {}
-
-    def get(self, tag: str, shape, dtype, device) -> torch.Tensor:
-        key = (tag, tuple(shape), dtype, str(device))
-        if key not in self.bufs:
-            self.bufs[key] = torch.empty(shape, dtype=dtype, device=device)
-        return self.bufs[key]
-
-
-_staging = _HostStaging()
-
-
 def skinny_gemm_fp8_host(A: torch.Tensor, B: torch.Tensor, scale_a: torch.Tensor, scale_b: torch.Tensor,
                          out: torch.Tensor, device="cuda") -> torch.Tensor:
-    """Same contraction with HOST (ideally pinned) tensors: copies every input
-    to the device, runs the kernel and copies the bf16 result back into
-    ``out``; everything is queued on the current stream and the call returns
-    after the result has arrived."""
+    """Same contraction with HOST (ideally pinned) tensors through
+    ``rdb_skinny_gemm_fp8_host``: the library copies every input to the device,
+    runs the kernel and copies the bf16 result back into ``out``; everything is
+    queued on the current stream and the call returns after the result has
+    arrived."""
     dev = torch.device(device)
-    dA = _staging.get("A", A.shape, torch.uint8, dev)
-    dB = _staging.get("B", B.shape, torch.uint8, dev)
-    dsa = _staging.get("sa", (1,), torch.float32, dev)
-    dsb = _staging.get("sb", (1,), torch.float32, dev)
-    dD = _staging.get("D", out.shape, torch.bfloat16, dev)
-    dA.copy_(_u8(A), non_blocking=True)
-    dB.copy_(_u8(B), non_blocking=True)
-    dsa.copy_(scale_a, non_blocking=True)
-    dsb.copy_(scale_b, non_blocking=True)
-    skinny_gemm_fp8(dA, dB, dsa, dsb, out=dD)
-    out.copy_(dD, non_blocking=True)
-    torch.cuda.current_stream(dev).synchronize()
+    A, B = _u8(A), _u8(B)
+    assert not A.is_cuda and not B.is_cuda and not out.is_cuda, "host tensors expected"
+    assert A.is_contiguous() and B.stride(1) == 1 and out.is_contiguous() and out.dtype == torch.bfloat16
+    M, K = A.shape
+    N = B.shape[0]
+    with torch.cuda.device(dev):
+        code = lib().rdb_skinny_gemm_fp8_host(A.data_ptr(), B.data_ptr(), scale_a.data_ptr(), scale_b.data_ptr(),
+                                              out.data_ptr(), M, N, K, B.stride(0), _stream_ptr(dev))
+    check(code, "rdb_skinny_gemm_fp8_host")
     return out

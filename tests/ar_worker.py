@@ -49,6 +49,19 @@ def main():
                 view = ar.all_reduce_in_workspace(xs[rank].to(dev))
                 torch.cuda.synchronize()
                 assert np.array_equal(view.cpu().view(torch.int16).numpy().view(np.uint16), want)
+    # results delivered straight into registered buffers (no copy out of the workspace)
+    reg = ar.new_result_buffer(4096 * 8192)
+    for n, off in ((8192, 0), (128 * 8192, 1 << 20), (513 * 8192 + 128, 0), (4096 * 8192, 0)):
+        for rep in range(2):
+            xs = [torch.randn(n, generator=torch.Generator().manual_seed(7000 * rep + 13 * r + n)).bfloat16()
+                  for r in range(world)]
+            out = ar.all_reduce(xs[rank].to(dev), out=reg[off:off + n], algo=2)
+            torch.cuda.synchronize()
+            assert R.lib().rdb_device_status() == 0, "device-side wait timed out"
+            want = O.allreduce_fp8(np.stack([x.view(torch.int16).numpy().view(np.uint16) for x in xs]))[0]
+            got = out.cpu().view(torch.int16).numpy().view(np.uint16)
+            assert np.array_equal(got, want), f"rank {rank} registered n {n} rep {rep}: {(got != want).sum()} differ"
+            dist.barrier()               # nobody starts the next call while a rank still reads this result
     dist.barrier()
     ar.close()
     dist.destroy_process_group()

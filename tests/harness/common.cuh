@@ -109,8 +109,10 @@ void bench_protocol(int warmups, int iterations, F&& launch) {
         CUDA_CHECK(cudaEventSynchronize(stop));
         float ms = 0.f;
         CUDA_CHECK(cudaEventElapsedTime(&ms, start, stop));
+        // fixed notation: the reference's parser cuts the last three characters of the output
+        // (bench.py:49), which must leave a number behind
         if (it == warmups) printf("End of warmup, ");
-        printf("%g, ", ms * 1000.0f);
+        printf("%.4f, ", ms * 1000.0f);
     }
     int st = rdb_device_status();
     if (st != 0) { fprintf(stderr, "device status %d\n", st); exit(1); }

@@ -1,6 +1,7 @@
 // argv: m n k.  Four distinct weight matrices rotate (projects/skinny_gemm/
 // bench.cu:42,53-60 in the reference), L2 flushed before every timed launch.
 #include "common.cuh"
+#include "rocm_dev_b200_compat.hpp"   // the reference-named launchers
 
 int main(int argc, char** argv) {
     if (argc != 4) return 2;
@@ -12,7 +13,7 @@ int main(int argc, char** argv) {
     float* dOne = to_device(one);
     uint16_t* dD = device_zeros<uint16_t>(static_cast<size_t>(m) * n);
     bench_protocol(20, 100, [&](int it) {
-        RDB_CHECK(rdb_skinny_gemm_fp8(dA, dB + static_cast<size_t>(it % batch) * n * k, dOne, dOne, dD, m, n, k, k, nullptr));
+        if (skinny_gemm_fastpath(dA, dB + static_cast<size_t>(it % batch) * n * k, dD, dOne, m, n, k) != SUCCESS) exit(1);
     });
     return 0;
 }

@@ -1,6 +1,7 @@
 // argv: m n k.  Random fp8 operands and one random scale (as the reference's
 // driver, projects/skinny_gemm/test.cu:43-114), CPU oracle vs the library.
 #include "common.cuh"
+#include "rocm_dev_b200_compat.hpp"   // the reference-named launchers
 
 int main(int argc, char** argv) {
     if (argc != 4) return 2;
@@ -13,7 +14,7 @@ int main(int argc, char** argv) {
     uint8_t *dA = to_device(hA), *dB = to_device(hB);
     float *dS = to_device(hs), *dOne = to_device(one);
     uint16_t* dD = device_zeros<uint16_t>(static_cast<size_t>(m) * n);
-    RDB_CHECK(rdb_skinny_gemm_fp8(dA, dB, dS, dOne, dD, m, n, k, k, nullptr));
+    if (skinny_gemm_fastpath(dA, dB, dD, dS, m, n, k) != SUCCESS) return 1;
     CUDA_CHECK(cudaDeviceSynchronize());
     auto got = to_host(dD, static_cast<size_t>(m) * n);
     std::vector<float> g(got.size()), r(got.size());

@@ -263,7 +263,84 @@ def test_error_codes(cuda_device):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_emulated_ranks_deliver_into_registered_buffers(cuda_device, oracle, world):
+    """Two-shot calls whose `out` lies in the registered result buffers: every
+    rank stores its reduced shard straight into all ranks' buffers (no copy out
+    of the workspace); same bits, also at an offset and next to unregistered calls."""
+    import rocm_dev_b200 as R
+    cap = 1 << 20
+    lr = R.LocalRanks(world, max_elems=cap, device=cuda_device)
+    try:
+        bufs = lr.new_result_buffers(cap)
+        for n, off in ((128, 0), (640, 512), (128 * 517, 1024), (cap, 0)):
+            for rep in range(2):
+                xs = [torch.randn(n, generator=torch.Generator().manual_seed(31 * rep + r + n)).bfloat16() for r in range(world)]
+                for b in bufs:
+                    b.zero_()
+                outs = lr.all_reduce([x.to(cuda_device) for x in xs], algo=2, outs=[b[off:off + n] for b in bufs])
+                torch.cuda.synchronize()
+                assert R.lib().rdb_device_status() == 0
+                want, _, _ = oracle.allreduce_fp8(np.stack([_bits(x) for x in xs]))
+                for r in range(world):
+                    assert np.array_equal(_bits(outs[r]), want), (world, n, rep, r)
+                    assert not bufs[r][:off].any() and not bufs[r][off + n:].any()   # nothing outside the window
+                plain = lr.all_reduce([x.to(cuda_device) for x in xs], algo=2)       # ordinary buffers still work
+                assert np.array_equal(_bits(plain[0]), want)
+    finally:
+        lr.close()
+
+
+@pytest.mark.gpu
+def test_a_wait_that_runs_out_is_reported_and_leaves_everything_usable(cuda_device, oracle):
+    """Failure detection without a fault: with a 2 ms wait budget, rank 0's
+    reduce step is issued while rank 1's encoded blocks are withheld by the
+    host.  The wait gives up by construction: the kernel returns, the status
+    word says RDB_DEVICE_TIMEOUT, rank 0 publishes its delivery flag marked
+    failed, and rank 1 - which does everything right, only late - sees that mark
+    and reports the failure as well instead of copying a shard that was never
+    written.  With the budget restored the same contexts then give bit-exact
+    results (both staging sets)."""
+    import rocm_dev_b200 as R
+    from rocm_dev_b200._lib import check
+    L = R.lib()
+    n = 128 * 64
+    lr = R.LocalRanks(2, max_elems=1 << 16, device=cuda_device)
+    try:
+        xs = [torch.randn(n, generator=torch.Generator().manual_seed(r)).bfloat16().to(cuda_device) for r in range(2)]
+        outs = [torch.zeros(n, dtype=torch.bfloat16, device=cuda_device) for _ in range(2)]
+        stream = torch.cuda.current_stream().cuda_stream
+        with torch.cuda.device(cuda_device):
+            assert L.rdb_set_wait_budget_ns(2_000_000) == 0
+            try:
+                epoch = {int(L.rdb_ar_begin_call(c)) for c in lr.ctx}.pop()
+                args = lambda r: (xs[r].data_ptr(), outs[r].data_ptr(), n, 2, stream)   # noqa: E731
+                check(L.rdb_ar_phase(lr.ctx[0], 1, epoch, *args(0)), "push 0")
+                check(L.rdb_ar_phase(lr.ctx[0], 2, epoch, *args(0)), "reduce 0")       # rank 1 has not pushed
+                torch.cuda.synchronize()
+                assert L.rdb_device_status() == 10                                      # reported, kernel returned
+                assert L.rdb_device_status() == 0                                       # reading clears it
+                check(L.rdb_ar_phase(lr.ctx[1], 1, epoch, *args(1)), "push 1")
+                check(L.rdb_ar_phase(lr.ctx[1], 2, epoch, *args(1)), "reduce 1")
+                check(L.rdb_ar_phase(lr.ctx[1], 3, epoch, *args(1)), "gather 1")
+                check(L.rdb_ar_phase(lr.ctx[0], 3, epoch, *args(0)), "gather 0")
+                torch.cuda.synchronize()
+                assert L.rdb_device_status() == 10                                      # rank 0's failure mark was seen
+                assert not outs[1].any() and not outs[0].any()                          # nobody copied a partial result
+            finally:
+                assert L.rdb_set_wait_budget_ns(1_000_000_000) == 0
+        for rep in range(2):                                                            # GPU and contexts are reusable
+            got = lr.all_reduce(xs, algo=2)
+            torch.cuda.synchronize()
+            assert L.rdb_device_status() == 0
+            want, _, _ = oracle.allreduce_fp8(np.stack([_bits(x) for x in xs]))
+            assert np.array_equal(_bits(got[0]), want) and np.array_equal(_bits(got[1]), want)
+    finally:
+        lr.close()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("backend", ["ipc", "symm"])
 def test_one_process_per_gpu(cuda_device, backend, world):
     """Real peer-to-peer path: one process per GPU; workspaces shared by CUDA

@@ -100,6 +100,80 @@ def test_config2_smallest_size_sampled(cuda_device, oracle):
     check_gemm_parity(bf16_bits(out[torch.from_numpy(rows).to(dev)]), ref, ref64, mag, K)
 
 
+def _config2_operands(n, dev, seed, rows=None):
+    """A, B ~ N(0,1) quantised per tensor (config 2), drawn and quantised on the GPU."""
+    from rocm_dev_b200 import quant
+    g = torch.Generator(device=dev).manual_seed(seed)
+    Aq, sa = quant.quantize_per_tensor(torch.randn((n if rows is None else rows, n), generator=g, device=dev).bfloat16())
+    Bq, sb = quant.quantize_per_tensor(torch.randn((n, n), generator=g, device=dev).bfloat16())
+    return Aq, Bq, sa, sb
+
+
+@pytest.mark.parametrize("n", [8192, 16384])
+def test_config2_larger_sizes_sampled(cuda_device, oracle, n):
+    """8192^3 and 16384^3 (config 2) through the automatic tiling - the CTA-pair kernel:
+    the oracle checks sixteen rows spread over first / interior / last tiles and both CTAs of a pair."""
+    import rocm_dev_b200 as R
+    dev = cuda_device
+    Aq, Bq, sa, sb = _config2_operands(n, dev, seed=n)
+    out = R.dense_gemm_fp8(Aq, Bq, sa, sb)
+    torch.cuda.synchronize()
+    assert R.lib().rdb_device_status() == 0
+    rows = np.r_[0:2, 127:130, 255:258, n // 2 - 1:n // 2 + 2, n - 130:n - 128, n - 3:n]
+    Bh = Bq.cpu().numpy()
+    Ah = Aq[torch.from_numpy(rows).to(dev)].cpu().numpy()
+    ref = oracle.gemm_fp8_bf16(Ah, Bh, sa.item(), sb.item())
+    ref64, mag = oracle.gemm_fp8_f64(Ah, Bh, sa.item(), sb.item())
+    check_gemm_parity(bf16_bits(out[torch.from_numpy(rows).to(dev)]), ref, ref64, mag, n)
+
+
+def test_rows_sharded_over_two_gpus(cuda_device, oracle):
+    """Config 2's multi-GPU form: the M rows of A and D are split over the GPUs, B is replicated, nothing is
+    communicated.  Each GPU's rows are checked against the oracle on its rows of A."""
+    import rocm_dev_b200 as R
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    n, world = 4096, 2
+    Aq, Bq, sa, sb = _config2_operands(n, cuda_device, seed=77)
+    Bh = Bq.cpu().numpy()
+    for r in range(world):
+        dev = torch.device("cuda", r)
+        lo, hi = r * n // world, (r + 1) * n // world
+        with torch.cuda.device(dev):
+            out = R.dense_gemm_fp8(Aq[lo:hi].to(dev).contiguous(), Bq.to(dev), sa.to(dev), sb.to(dev))
+            torch.cuda.synchronize(dev)
+            assert R.lib().rdb_device_status() == 0
+        rows = np.r_[0:3, 255:258, hi - lo - 3:hi - lo]
+        Ah = Aq[lo:hi][torch.from_numpy(rows).to(cuda_device)].cpu().numpy()
+        ref = oracle.gemm_fp8_bf16(Ah, Bh, sa.item(), sb.item())
+        ref64, mag = oracle.gemm_fp8_f64(Ah, Bh, sa.item(), sb.item())
+        check_gemm_parity(bf16_bits(out[torch.from_numpy(rows).to(dev)]), ref, ref64, mag, n)
+
+
+def test_fp32_output_at_a_4_byte_aligned_address(cuda_device, oracle):
+    """A D that is only 4-byte aligned (a view into a larger buffer) takes scalar stores; both kernels."""
+    import rocm_dev_b200 as R
+    dev = cuda_device
+    m, n, k = 256, 512, 256
+    g = torch.Generator().manual_seed(21)
+    A = torch.randint(0, 0x60, (m, k), generator=g, dtype=torch.uint8)
+    B = torch.randint(0, 0x60, (n, k), generator=g, dtype=torch.uint8)
+    ref32 = oracle.gemm_fp8_f32(A.numpy(), B.numpy())
+    ref64, mag = oracle.gemm_fp8_f64(A.numpy(), B.numpy(), 1.0, 1.0)
+    tol = 4 * np.sqrt(k) * 2.0 ** -24 * mag + 1e-30
+    dA, dB = A.to(dev), B.to(dev)
+    for off in (1, 2, 3):
+        buf = torch.full((m * n + 4,), -7.0, dtype=torch.float32, device=dev)
+        D = buf[off:off + m * n]
+        assert R.lib().rdb_dense_gemm_fp8_f32(dA.data_ptr(), dB.data_ptr(), D.data_ptr(), m, n, k, 0) == 0
+        torch.cuda.synchronize()
+        assert R.lib().rdb_device_status() == 0
+        got = D.cpu().numpy().reshape(m, n).astype(np.float64)
+        assert (np.abs(got - ref64) <= tol).all()
+        assert (buf[:off] == -7.0).all() and (buf[off + m * n:] == -7.0).all()      # nothing outside D
+    assert ref32.shape == (m, n)
+
+
 def test_full_size_properties(cuda_device):
     """8192^3: size-independent properties - a power-of-two scale commutes
     exactly, the product with an identity-like B copies A's values, and two runs

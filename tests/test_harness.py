@@ -52,6 +52,64 @@ def test_project_flow_with_a_stand_in_compiler(tmp_path, monkeypatch):
         harness.Project("missing", str(root))
 
 
+def _driver_formats():
+    """The printf formats the real drivers use (tests/harness/common.cuh), so
+    that the stand-in executables below print exactly what they print."""
+    import re
+    src = open(os.path.join(HARNESS, "common.cuh")).read()
+    sample = re.search(r'printf\("(%[.0-9a-z]+, )", ms \* 1000.0f\)', src).group(1)
+    warm = re.search(r'printf\("(End of warmup, )"\)', src).group(1)
+    deltas = re.search(r'printf\("(\{.*?\})", mx, tot\)', src).group(1).replace('\\"', '"')
+    return sample, warm, deltas
+
+
+def test_the_reference_harness_itself_accepts_the_drivers_output(tmp_path):
+    """The reference's OWN bench.py and class_project.py, unmodified (located
+    through RDB_REFERENCE_ROOT, copied next to a projects/ directory, never
+    committed), run against executables that print what this repository's
+    drivers print: its test parser (bench.py:31-44) and its time parser
+    `time_string[2:-3].split(", ")[3:]` (bench.py:49-56) accept the output and
+    the summary and the record come out right."""
+    import subprocess
+    import sys
+    ref = os.environ.get("RDB_REFERENCE_ROOT", "/root/reference")
+    if not (os.path.isfile(os.path.join(ref, "bench.py")) and os.path.isfile(os.path.join(ref, "class_project.py"))):
+        pytest.skip("reference harness not available on this machine")
+    sample_fmt, warm_token, delta_fmt = _driver_formats()
+    root = tmp_path
+    for f in ("bench.py", "class_project.py"):
+        shutil.copy(os.path.join(ref, f), root / f)
+    (root / "projects" / "demo").mkdir(parents=True)
+    (root / "projects" / "demo" / "test.cu").write_text("// test")
+    (root / "projects" / "demo" / "bench.cu").write_text("// bench")
+    (root / "build").mkdir()
+    warm, timed = [31.5, 20.25, 19.0, 18.5, 18.25], [12.5, 12.25, 12.75, 12.0]
+    bench_out = "".join(sample_fmt % v for v in warm) + warm_token + "".join(sample_fmt % v for v in timed)
+    test_out = delta_fmt % (0.0625, 1.5)
+    (root / "expected_test.txt").write_text(test_out)
+    (root / "expected_bench.txt").write_text(bench_out)
+    bindir = root / "bin"
+    bindir.mkdir()
+    fake = bindir / "hipcc"             # "compiles" <file> to a script that prints the recorded driver output
+    fake.write_text('#!/bin/bash\nout="${@: -1}"\nsrc="$2"\nkind=test; [[ "$src" == *bench.cu ]] && kind=bench\n'
+                    f'printf \'#!/bin/bash\\ncat "{root}/expected_%s.txt"\\n\' "$kind" > "$out"\nchmod +x "$out"\n')
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    env = dict(os.environ, PATH=f"{bindir}:{os.environ['PATH']}")
+    res = subprocess.run([sys.executable, "bench.py", "-p", "demo", "-a", "8 64 64", "-t", "2", "-m", "drop-in"], cwd=root, env=env,
+                         capture_output=True, text=True, timeout=120)
+    assert res.returncode == 0, res.stdout + res.stderr
+    data = json.loads(res.stdout[res.stdout.index("{"):])
+    # the reference's parser drops the last character of the last sample (12.0000 -> 12.000): same value
+    assert data["median"] == pytest.approx(12.375) and data["mean"] == pytest.approx(12.375) and data["message"] == "drop-in"
+    assert data["max_deltas"].startswith("0.0625 <- [0.0625, 0.0625]")
+    recs = list((root / "data" / "demo").glob("*.json"))
+    assert len(recs) == 1 and json.loads(recs[0].read_text())["8 64 64"][0]["median"] == pytest.approx(12.375)
+    # and this repository's mirror of the harness reads the same output the same way
+    w, t = harness.parse_bench_output(bench_out)
+    assert t == timed and w == warm
+    assert harness.parse_test_output(test_out) == (0.0625, 1.5)
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("project,args,tol", [("skinny_gemm", "8 1024 1024", 0.01), ("async_gemm_16x16x64", "64 64 256", 1e-3),
                                               ("async_gemm_blanes", "32 96 128", 1e-3), ("async_gemm_sparse", "8 64 64", 1e-3),

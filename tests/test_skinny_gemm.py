@@ -62,7 +62,7 @@ def test_config0_shape_all_m(cuda_device, oracle, M):
 
 
 @pytest.mark.parametrize("N,K", [(6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336)])
-@pytest.mark.parametrize("M", [1, 8, 16, 32])
+@pytest.mark.parametrize("M", [1, 2, 4, 8, 16, 32])
 def test_decode_sweep_shapes(cuda_device, oracle, M, N, K):
     _parity(oracle, cuda_device, M, N, K, seed=M)
 
@@ -90,6 +90,107 @@ def test_every_cluster_size_gives_the_same_answer(cuda_device, oracle, split_k):
     ref = oracle.gemm_fp8_bf16(Aq.numpy(), Bq.numpy(), sa.item(), 1.0)
     ref64, mag = oracle.gemm_fp8_f64(Aq.numpy(), Bq.numpy(), sa.item(), 1.0)
     check_gemm_parity(bf16_bits(D), ref, ref64, mag, K)
+
+
+# ------------------------------------------------------------ grouped entry
+def _grouped(oracle, dev, shapes, seed=0, pitch=None):
+    """Runs `shapes` = [(M, N, K), ...] as ONE grouped launch and checks every
+    problem against the oracle with the stated tolerance."""
+    import rocm_dev_b200 as R
+    from rocm_dev_b200 import quant
+    host, problems = [], []
+    for i, (M, N, K) in enumerate(shapes):
+        Aq, Bq, sa, sb = quant.synthetic_gemm_operands(M, N, K, seed=seed + i)
+        host.append((Aq, Bq, sa, sb))
+        dB = Bq.to(dev)
+        if pitch:                                   # weights inside a wider allocation: row pitch > K
+            wide = torch.full((N, K + pitch), 0x7E, dtype=torch.uint8, device=dev)
+            wide[:, :K] = dB
+            dB = wide[:, :K]
+        D = torch.full((M, N), 77.0, dtype=torch.bfloat16, device=dev)      # overwritten, not accumulated into
+        problems.append((Aq.to(dev), dB, sa.to(dev), sb.to(dev), D))
+    assert R.skinny_gemm_fp8_grouped(problems) == 0
+    torch.cuda.synchronize()
+    assert R.lib().rdb_device_status() == 0
+    reports = []
+    for (M, N, K), (Aq, Bq, sa, sb), pr in zip(shapes, host, problems):
+        ref = oracle.gemm_fp8_bf16(Aq.numpy(), Bq.numpy(), sa.item(), sb.item())
+        ref64, mag = oracle.gemm_fp8_f64(Aq.numpy(), Bq.numpy(), sa.item(), sb.item())
+        reports.append(check_gemm_parity(bf16_bits(pr[4]), ref, ref64, mag, K))
+    return problems, reports
+
+
+def test_grouped_tiny_and_ragged_problems(cuda_device, oracle):
+    """Fewer units than CTAs (most CTAs idle, tiles shared by single-unit
+    ranges), ragged M / N / K, both activation paddings."""
+    _grouped(oracle, cuda_device, [(8, 64, 256), (3, 48, 144)])
+    _grouped(oracle, cuda_device, [(3, 130, 144), (7, 2, 16), (17, 1000, 272), (32, 258, 4112), (5, 126, 128),
+                                   (9, 384, 48), (1, 64, 8192)], seed=4)
+    _grouped(oracle, cuda_device, [(4, 300, 2048)], seed=9, pitch=256)
+
+
+@pytest.mark.parametrize("M", [1, 8, 32])
+def test_grouped_config0_shape(cuda_device, oracle, M):
+    """Config 0 (N = K = 8192) as a single-problem list: 128-row units, every tile shared by several CTAs."""
+    _, rep = _grouped(oracle, cuda_device, [(M, 8192, 8192)])
+    assert rep[0]["rel_fro"] < 1e-2
+
+
+@pytest.mark.parametrize("M", [1, 2, 4, 8, 16])
+def test_grouped_decode_layer(cuda_device, oracle, M):
+    """The four projections of one decode layer at one M, one launch."""
+    _grouped(oracle, cuda_device, [(M, 6144, 4096), (M, 4096, 4096), (M, 28672, 4096), (M, 4096, 14336)], seed=M)
+
+
+def test_grouped_whole_sweep_is_deterministic_and_replayable(cuda_device, oracle):
+    """All 20 (shape, M) cases of the decode sweep in one launch: parity for
+    every problem, identical bits when launched again and when replayed from a
+    CUDA graph (the launch keeps no state that a replay could see stale)."""
+    import rocm_dev_b200 as R
+    shapes = [(M, N, K) for M in (1, 2, 4, 8, 16) for (N, K) in ((6144, 4096), (4096, 4096), (28672, 4096), (4096, 14336))]
+    problems, _ = _grouped(oracle, cuda_device, shapes, seed=50)
+    first = [p[4].clone() for p in problems]
+    for p in problems:
+        p[4].zero_()
+    assert R.skinny_gemm_fp8_grouped(problems) == 0
+    torch.cuda.synchronize()
+    assert all(torch.equal(a, p[4]) for a, p in zip(first, problems))
+    stream = torch.cuda.Stream(device=cuda_device)
+    with torch.cuda.stream(stream):
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            assert R.skinny_gemm_fp8_grouped(problems) == 0
+        for _ in range(3):
+            for p in problems:
+                p[4].zero_()
+            g.replay()
+            g.replay()
+            torch.cuda.synchronize()
+            assert all(torch.equal(a, p[4]) for a, p in zip(first, problems))
+    assert R.lib().rdb_device_status() == 0
+
+
+def test_grouped_matches_the_plan_and_rejects_bad_lists(cuda_device):
+    import ctypes as C
+    import rocm_dev_b200 as R
+    from rocm_dev_b200.skinny_gemm import SkinnyProblem
+    rows, ranges = R.skinny_gemm_grouped_plan([(8, 6144, 4096), (8, 4096, 14336)], ctas=148)
+    assert rows == [256, 256] and ranges[0] == 0 and ranges[-1] == 24 * 32 + 16 * 112
+    assert all(b >= a for a, b in zip(ranges, ranges[1:])) and max(b - a for a, b in zip(ranges, ranges[1:])) <= 18
+    L = R.lib()
+    x = torch.zeros(4096, dtype=torch.uint8, device=cuda_device)
+    f = torch.ones(1, device=cuda_device)
+    ok = SkinnyProblem(x.data_ptr(), x.data_ptr(), f.data_ptr(), f.data_ptr(), x.data_ptr(), 8, 16, 64, 64)
+    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(ok), 0, 0) == 6
+    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(ok), 33, 0) == 6
+    bad = SkinnyProblem(x.data_ptr(), x.data_ptr(), f.data_ptr(), f.data_ptr(), x.data_ptr(), 33, 16, 64, 64)
+    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(bad), 1, 0) == 1
+    bad = SkinnyProblem(x.data_ptr(), x.data_ptr(), f.data_ptr(), f.data_ptr(), x.data_ptr(), 8, 15, 64, 64)
+    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(bad), 1, 0) == 2
+    bad = SkinnyProblem(x.data_ptr(), x.data_ptr(), f.data_ptr(), f.data_ptr(), x.data_ptr(), 8, 16, 40, 48)
+    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(bad), 1, 0) == 3
+    bad = SkinnyProblem(x.data_ptr() + 1, x.data_ptr(), f.data_ptr(), f.data_ptr(), x.data_ptr(), 8, 16, 64, 64)
+    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(bad), 1, 0) == 7
 
 
 def test_row_pitch_and_output_overwrite(cuda_device, oracle):
@@ -161,7 +262,9 @@ def test_torch_binding_mirror(cuda_device, oracle):
     Aq, Bq, sa, sb = quant.synthetic_gemm_operands(M, N, K, seed=12)
     dev = cuda_device
     D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
-    h = R.HFRK_skinny_gemm(1)
+    import hfrk_skinny_gemm                      # the module name callers of the reference import
+    assert hfrk_skinny_gemm.HFRK_skinny_gemm is R.HFRK_skinny_gemm
+    h = hfrk_skinny_gemm.HFRK_skinny_gemm(1)
     code = h.skinny_gemm_torch_binding(Aq.to(dev).view(torch.float8_e4m3fn), Bq.to(dev).view(torch.float8_e4m3fn).t(),
                                        D, sa.to(dev), 2, 1, 1, 1, 1, 4, 2)
     assert code == 0
