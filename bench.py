@@ -484,29 +484,36 @@ def bench_allreduce(torch, dist, R, dev, rank, world):
     ar = R.Fp8AllReduce(max_elems=4096 * 8192, backend=os.environ.get("RDB_AR_BACKEND", "auto"))
     reg = ar.new_result_buffer(4096 * 8192)
     out = {"unit": "GB/s busBW", "world": world, "workspace": ar.backend, "multimem_all_gather": ar.multicast,
+           "timing": "device time, max over ranks, median of 5 batches of back-to-back calls",
            "parity": allreduce_parity(torch, dist, R, ar, reg, dev, rank, world), "cases": {}}
 
-    def timed(fn, iters):
+    def timed(fn, iters, batches=5):
+        """Median over `batches` batches of the per-call device time (each batch: events around `iters`
+        back-to-back calls, max over ranks).  Single batches on these shared machines now and then come out
+        twice as slow for whichever collective is running - NCCL's included - so one mean is not reported."""
         for _ in range(3):
             fn()
-        torch.cuda.synchronize()
-        dist.barrier()
-        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        a.record()
-        for _ in range(iters):
-            fn()
-        b.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([a.elapsed_time(b) / iters], device=dev)
+        per_batch = []
+        for _ in range(batches):
+            torch.cuda.synchronize()
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                fn()
+            b.record()
+            torch.cuda.synchronize()
+            per_batch.append(a.elapsed_time(b) / iters)
+        t = torch.tensor(per_batch, device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item()) * 1e-3
+        return float(t.median().item()) * 1e-3
 
     for T in (1, 16, 128, 1024, 4096):
         n = T * 8192
         x = torch.randn(n, generator=torch.Generator(device=dev).manual_seed(rank), device=dev).bfloat16()
         y = torch.empty_like(x)
         z = x.clone()
-        iters = 200 if T <= 128 else 40
+        iters = 40 if T <= 128 else 10
         t_fp8 = timed(lambda: ar.all_reduce(x, out=y), iters)           # result into an ordinary buffer of the caller
         t_reg = timed(lambda: ar.all_reduce(x, out=reg[:n]), iters)     # result into the caller's registered buffer
         t_nccl = timed(lambda: dist.all_reduce(z), iters)
