@@ -31,10 +31,11 @@ SHAPES = [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 28672, 4096), ("do
 MS = [1, 2, 4, 8, 16]
 # DRAM bytes (read + write) per algorithmic byte, each from one ncu capture of that kernel; DRAM traffic grows in
 # proportion to the weight bytes, so the ratio is applied to the bytes of a launch.
-TRAFFIC_PER_ALGO_BYTE = {"skinny_gemm_kernel": 1.03, "skinny_grouped_kernel": 1.03}
+TRAFFIC_PER_ALGO_BYTE = {"skinny_gemm_kernel": 1.03, "skinny_grouped_kernel": 1.028}
 TRAFFIC_NOTE = {"skinny_gemm_kernel": "ncu capture of gate_up at M=8 (no split-K): 121.5 MB moved for 117.9 MB algorithmic; "
                                       "scaled by bytes",
-                "skinny_grouped_kernel": "ncu capture of one grouped launch of the four projections at M=8; scaled by bytes"}
+                "skinny_grouped_kernel": "ncu capture of one grouped launch of the four projections at M=8: 225.0 MB moved for "
+                                         "219.0 MB algorithmic; scaled by bytes"}
 METRIC = "skinny FP8 GEMM HBM GB/s, decode sweep M=1..16 over Llama-3-8B-shaped (N,K)"
 
 
@@ -57,7 +58,7 @@ def measured_peak():
 
 class ClockSampler:
     """Samples SM clock and throttle reasons (read-only NVML queries) every
-    10 ms on a thread while a region runs."""
+    few milliseconds on a thread while a region runs."""
     REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
 
     def __init__(self, index):
@@ -86,7 +87,7 @@ class ClockSampler:
                     except Exception as e:  # noqa: BLE001
                         self.error = str(e)
                         return
-                    time.sleep(0.01)
+                    time.sleep(0.002)
             self._thread = threading.Thread(target=loop, daemon=True)
             self._thread.start()
         except Exception as e:  # noqa: BLE001
@@ -179,13 +180,13 @@ def timed_graphs(torch, stream, graphs, steps, warmup, barrier=None, sampler=Non
     """Replays graphs[i % len] for `steps` timed iterations after `warmup`
     untimed ones; CUDA events on the launching stream.  Returns milliseconds."""
     with torch.cuda.stream(stream):
-        for w in range(warmup):
+        if sampler:
+            sampler.start()                  # clocks are sampled from the warm-up replays on: the same load, and
+        for w in range(warmup):              # the timed region alone can be shorter than one sampling interval
             graphs[w % len(graphs)].replay()
         torch.cuda.synchronize()
         if barrier:
             barrier()
-        if sampler:
-            sampler.start()
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.profiler.start()          # lets `ncu --profile-from-start off` see only the timed region
@@ -225,7 +226,7 @@ def run_gpu(args):
 
     # A grouped launch streams all of its problems at once, so each of them needs weights of its own for the
     # stream to stay L2-cold: one set of the four matrices per M, and two such groups alternating between steps.
-    weights, acts, outs = make_inputs(torch, quant, dev, sets=2 * len(MS))
+    weights, acts, outs = make_inputs(torch, quant, dev, sets=2 if args.single else 2 * len(MS))
     flags = R.OVERLAP_PRIOR_KERNEL   # weights are never written inside the timed region
 
     def problems_of(M, wset):
