@@ -42,7 +42,9 @@ typedef enum rdb_status {
     RDB_BAD_SHAPE = 8,                     /* non-positive or unsupported extent */
     RDB_CUDA_ERROR = 9,                    /* a CUDA runtime / driver call failed */
     RDB_DEVICE_TIMEOUT = 10,               /* a bounded device-side wait ran out */
-    RDB_SIZE_ABOVE_LIMIT = 11
+    RDB_SIZE_ABOVE_LIMIT = 11,
+    RDB_IO_ERROR = 12,                     /* a file could not be opened, read or written */
+    RDB_BAD_FILE = 13                      /* not a file of the expected format, truncated or corrupted */
 } rdb_status;
 
 /* Human-readable name of a status code (static storage). */
@@ -219,6 +221,31 @@ int rdb_sparse_gemm_fp8_tuned(const uint8_t *A, const uint8_t *Wvals, const uint
  * an unsupported shape). */
 size_t rdb_sparse_meta_bytes(int N, int K);
 int rdb_sparse_pack_2of4(const uint8_t *Wq, int N, int K, uint8_t *vals, uint8_t *meta);
+
+/* On-disk form of the compressed weights - values, metadata and the per-tensor
+ * scale in one file (64-byte header with magic "RDB24W", version, N, K, scale,
+ * section sizes and a checksum; then values [N,K/2]; then the metadata exactly
+ * as the kernel reads it), so that weights are pruned, quantised and packed
+ * once, offline.  Host code, no GPU.  The reference stores no sparse weights
+ * (its "sparse" project multiplies a dense B with constant indices,
+ * projects/async_gemm_sparse/consumer.cu:65,82-88), so there is no reference
+ * format to follow.
+ *   _write           writes vals / meta as produced by rdb_sparse_pack_2of4;
+ *                    RDB_INVALID_CONFIG if a metadata entry is not an ascending
+ *                    pair of positions.
+ *   _pack_and_write  the same from the uncompressed 2:4 bytes Wq [N,K];
+ *                    RDB_INVALID_CONFIG if Wq is not 2:4.
+ *   _info            header fields only (any output may be NULL).
+ *   _read            loads both sections into caller buffers of the given
+ *                    capacities; RDB_BAD_FILE for a wrong magic / version /
+ *                    size, a truncated or over-long file or a checksum mismatch,
+ *                    RDB_INVALID_CONFIG for an intact file whose metadata is not
+ *                    a 2:4 selection, RDB_SIZE_ABOVE_LIMIT if a buffer is too
+ *                    small, RDB_IO_ERROR if the file cannot be opened. */
+int rdb_sparse_file_write(const char *path, const uint8_t *vals, const uint8_t *meta, float scale, int N, int K);
+int rdb_sparse_file_pack_and_write(const char *path, const uint8_t *Wq, float scale, int N, int K);
+int rdb_sparse_file_info(const char *path, int *N, int *K, float *scale);
+int rdb_sparse_file_read(const char *path, uint8_t *vals, size_t vals_capacity, uint8_t *meta, size_t meta_capacity);
 
 /* ---------------------------------------------------------- sum reduce
  * D[m,n] = sum over the batch of (A[i,m,n] + B[i,m,n]), fp32, summed in batch

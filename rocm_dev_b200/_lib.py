@@ -39,6 +39,10 @@ _SIGNATURES = {
     "rdb_sparse_gemm_fp8_tuned": (i, [u8p, u8p, u8p, f32p, f32p, vp, i, i, i, i, vp]),
     "rdb_sparse_meta_bytes": (C.c_size_t, [i, i]),
     "rdb_sparse_pack_2of4": (i, [vp, i, i, vp, vp]),
+    "rdb_sparse_file_write": (i, [C.c_char_p, vp, vp, C.c_float, i, i]),
+    "rdb_sparse_file_pack_and_write": (i, [C.c_char_p, vp, C.c_float, i, i]),
+    "rdb_sparse_file_info": (i, [C.c_char_p, vp, vp, vp]),
+    "rdb_sparse_file_read": (i, [C.c_char_p, vp, C.c_size_t, vp, C.c_size_t]),
     "rdb_tiled_sum_reduce": (i, [vp, vp, vp, i, i, i, vp]),
     "rdb_globs": (i, [vp, vp]),
     "rdb_globs_n": (i, [vp, i, i, i, vp]),

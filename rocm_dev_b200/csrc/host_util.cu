@@ -105,6 +105,8 @@ const char* rdb_status_string(int status) {
         case RDB_CUDA_ERROR: return "CUDA call failed";
         case RDB_DEVICE_TIMEOUT: return "device-side wait timed out";
         case RDB_SIZE_ABOVE_LIMIT: return "size above the supported limit";
+        case RDB_IO_ERROR: return "file could not be opened, read or written";
+        case RDB_BAD_FILE: return "not a valid file of this format (wrong magic or version, truncated, or corrupted)";
         default: return "unknown status";
     }
 }

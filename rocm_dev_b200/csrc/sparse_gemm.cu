@@ -377,6 +377,10 @@ int rdb_sparse_pack_2of4(const uint8_t* Wq, int N, int K, uint8_t* vals, uint8_t
             *dst |= (c & 1) ? static_cast<uint8_t>(nib << 4) : nib;
         }
     }
+    // rows past N in the last tile (their values are never loaded): a valid selection, positions (0, 1)
+    for (int n = N; n < tiles * 128; n++)
+        for (int a = 0; a < atoms; a++)
+            memset(meta + ((static_cast<size_t>(n / 128) * atoms + a) * 128 + (n % 128)) * 16, 0x44, 16);
     return RDB_SUCCESS;
 }
 

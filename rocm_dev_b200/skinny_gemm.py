@@ -36,6 +36,8 @@ class SkinnyGemmReturnCode(enum.IntEnum):
     CUDA_ERROR = 9
     DEVICE_TIMEOUT = 10
     SIZE_ABOVE_LIMIT = 11
+    IO_ERROR = 12
+    BAD_FILE = 13
 
 
 _ones: dict[int, torch.Tensor] = {}

@@ -42,6 +42,32 @@ def pack_2of4(Wq: torch.Tensor):
     return vals, meta
 
 
+def save_2of4(path: str, vals: torch.Tensor, meta: torch.Tensor, scale: float) -> None:
+    """Writes compressed weights (as returned by ``pack_2of4``) and their
+    per-tensor scale as one file (rdb_sparse_file_write)."""
+    import ctypes as C
+    assert vals.dtype == torch.uint8 and meta.dtype == torch.uint8 and not vals.is_cuda and not meta.is_cuda
+    vals, meta = vals.contiguous(), meta.contiguous()
+    N, K2 = vals.shape
+    check(lib().rdb_sparse_file_write(str(path).encode(), vals.data_ptr(), meta.data_ptr(), C.c_float(float(scale)), N, 2 * K2),
+          "rdb_sparse_file_write")
+
+
+def load_2of4(path: str):
+    """Reads a file written by ``save_2of4``: (vals [N,K/2] uint8, meta uint8, scale).
+    Raises RdbError for a file that is not of this format, is damaged or does
+    not hold a 2:4 selection."""
+    import ctypes as C
+    n, k, sc = C.c_int(), C.c_int(), C.c_float()
+    check(lib().rdb_sparse_file_info(str(path).encode(), C.byref(n), C.byref(k), C.byref(sc)), "rdb_sparse_file_info")
+    N, K = n.value, k.value
+    vals = torch.empty((N, K // 2), dtype=torch.uint8)
+    meta = torch.empty(int(lib().rdb_sparse_meta_bytes(N, K)), dtype=torch.uint8)
+    check(lib().rdb_sparse_file_read(str(path).encode(), vals.data_ptr(), vals.numel(), meta.data_ptr(), meta.numel()),
+          "rdb_sparse_file_read")
+    return vals, meta, sc.value
+
+
 def sparse_gemm_fp8(A: torch.Tensor, vals: torch.Tensor, meta: torch.Tensor, scale_a: torch.Tensor,
                     scale_b: torch.Tensor, out: torch.Tensor | None = None, split_k: int = 0) -> torch.Tensor:
     """D[M,N] = bf16((A . W^T) * scale_a * scale_b) with W given compressed."""

@@ -51,6 +51,85 @@ def test_packer_matches_oracle_compressor(oracle):
         R.pack_2of4(dense)
 
 
+def test_file_round_trip_and_rejections(tmp_path, oracle):
+    """The on-disk form of packed 2:4 weights: what is written comes back bit for
+    bit with its shape and scale; files that are not of the format, are damaged,
+    or do not hold a 2:4 selection are refused with the documented codes."""
+    import struct
+    import rocm_dev_b200 as R
+    N, K = 200, 512                                   # a last tile with fewer than 128 rows
+    Wq, sb = _sparse_weights(N, K, 3)
+    vals, meta = R.pack_2of4(Wq)
+    path = tmp_path / "w.rdb24"
+    R.save_2of4(path, vals, meta, sb.item())
+    raw = path.read_bytes()
+    assert raw[:6] == b"RDB24W" and struct.unpack_from("<II", raw, 8) == (1, 64)
+    assert struct.unpack_from("<ii", raw, 16) == (N, K) and len(raw) == 64 + vals.numel() + meta.numel()
+    v2, m2, s2 = R.load_2of4(path)
+    assert torch.equal(v2, vals) and torch.equal(m2, meta)
+    assert np.float32(s2).tobytes() == sb.numpy().tobytes()
+    # expanding what was read gives back the pruned matrix (the oracle's expander is the checker)
+    m = m2.numpy().reshape(-1, K // 128, 128, 16)
+    per_group = np.stack([m & 0xF, m >> 4], axis=-1).reshape(-1, K // 128, 128, 32).transpose(0, 2, 1, 3).reshape(-1, K // 4)[:N]
+    back = oracle.expand_2of4(v2.numpy(), per_group)
+    nz = (Wq.numpy() & 0x7F) != 0
+    assert np.array_equal(back[nz], Wq.numpy()[nz]) and not (back[~nz] & 0x7F).any()
+    # straight from the uncompressed bytes, and the refusal of a matrix that is not 2:4
+    L = R.lib()
+    p2 = tmp_path / "direct.rdb24"
+    assert L.rdb_sparse_file_pack_and_write(str(p2).encode(), Wq.data_ptr(), sb.item(), N, K) == 0
+    assert p2.read_bytes() == raw
+    dense = Wq.clone()
+    dense[7, 8:12] = 0x38
+    assert L.rdb_sparse_file_pack_and_write(str(tmp_path / "no.rdb24").encode(), dense.data_ptr(), 1.0, N, K) == 6
+
+    def refused(mutated: bytes) -> int:
+        q = tmp_path / "bad.rdb24"
+        q.write_bytes(mutated)
+        try:
+            R.load_2of4(q)
+        except R.RdbError as e:
+            return e.code
+        return 0
+
+    assert refused(b"NOTRDB24" + raw[8:]) == 13                                   # magic
+    assert refused(raw[:8] + struct.pack("<I", 2) + raw[12:]) == 13               # version
+    assert refused(raw[:-100]) == 13                                              # truncated
+    assert refused(raw + b"x") == 13                                              # trailing bytes
+    flipped = bytearray(raw)
+    flipped[64 + 1000] ^= 0x10
+    assert refused(bytes(flipped)) == 13                                          # checksum
+    assert refused(raw[:16] + struct.pack("<i", N + 1) + raw[20:]) == 13          # header disagrees with the sizes
+    # an intact file (valid checksum) whose metadata is not an ascending pair per group: not a 2:4 selection
+    bad_meta = bytearray(raw)
+    bad_meta[64 + vals.numel()] = 0x00                                           # idx0 == idx1 == 0
+    h = 1469598103934665603
+    for b in bytes(bad_meta[64:]):
+        h = ((h ^ b) * 1099511628211) & 0xFFFFFFFFFFFFFFFF
+    bad_meta[48:56] = struct.pack("<Q", h)
+    assert refused(bytes(bad_meta)) == 6
+    assert L.rdb_sparse_file_write(str(tmp_path / "w2").encode(), vals.data_ptr(), bytes(bad_meta[64 + vals.numel():]), 1.0, N, K) == 6
+    with pytest.raises(R.RdbError) as e:
+        R.load_2of4(tmp_path / "missing.rdb24")
+    assert e.value.code == 12
+
+
+@pytest.mark.gpu
+def test_weights_loaded_from_a_file_give_the_same_product(cuda_device, oracle, tmp_path):
+    import rocm_dev_b200 as R
+    from rocm_dev_b200 import quant
+    M, N, K = 16, 512, 1024
+    Wq, sb = _sparse_weights(N, K, 5)
+    vals, meta = R.pack_2of4(Wq)
+    R.save_2of4(tmp_path / "w.rdb24", vals, meta, sb.item())
+    v2, m2, s2 = R.load_2of4(tmp_path / "w.rdb24")
+    Aq, sa = quant.quantize_per_tensor(torch.randn((M, K), generator=torch.Generator().manual_seed(6)).bfloat16())
+    dev = cuda_device
+    a = R.sparse_gemm_fp8(Aq.to(dev), vals.to(dev), meta.to(dev), sa.to(dev), sb.to(dev))
+    b = R.sparse_gemm_fp8(Aq.to(dev), v2.to(dev), m2.to(dev), sa.to(dev), torch.tensor([s2], device=dev))
+    assert torch.equal(a, b)
+
+
 def _check(oracle, dev, M, N, K, seed=0, split_k=0):
     import rocm_dev_b200 as R
     from rocm_dev_b200 import quant
