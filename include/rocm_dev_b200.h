@@ -121,6 +121,24 @@ int rdb_skinny_gemm_fp8_tuned(const uint8_t *A, const uint8_t *B, const float *s
  * knobs of projects/skinny_gemm/core.cu:29-38. */
 int rdb_skinny_gemm_plan(int M, int N, int K, int sm_count, int *rows_per_tile, int *split_k, int *stages);
 
+/* Tuning table: measured best configurations per shape, consulted by
+ * rdb_skinny_gemm_fp8 / _hinted (when given no knobs), rdb_skinny_gemm_plan and
+ * rdb_dense_gemm_fp8 / _f32 before their analytic plans.  Written by the tuner
+ * (python -m rocm_dev_b200.tuner --table FILE), loaded from a text file - lines
+ * "skinny <m_bucket 16|32> <N> <K> <rows_per_tile> <split_k> <stages>" and
+ * "dense <M> <N> <K> <tile_rows 128|256|2> <max_ctas>", 0 = automatic for a
+ * knob, '#' comments - either explicitly or, on first use, from the file the
+ * environment variable RDB_TUNING_TABLE names.  Process-wide, thread-safe; a
+ * later entry for the same shape replaces the earlier one; a file with a bad
+ * line is refused as a whole (RDB_BAD_FILE).  The reference's counterpart is
+ * the configuration its tuner compiles in (grid.py:106-116 rewriting
+ * projects/<name>/core.cu). */
+int rdb_tuning_table_load(const char *path);
+int rdb_tuning_table_set_skinny(int M, int N, int K, int rows_per_tile, int split_k, int stages);
+int rdb_tuning_table_set_dense(int M, int N, int K, int tile_rows, int max_ctas);
+int rdb_tuning_table_clear(void);
+int rdb_tuning_table_size(void);
+
 /* Number of clusters of cluster_size skinny-GEMM CTAs, each with smem_bytes of
  * dynamic shared memory, that the current device can hold at once (the
  * planner keeps every launch inside one such wave); -1 on error.  The

@@ -26,6 +26,11 @@ _SIGNATURES = {
     "rdb_skinny_gemm_fp8_host": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, vp]),
     "rdb_skinny_gemm_fp8_hinted": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, i, i, i, i, i, i, i, i, vp]),
     "rdb_skinny_gemm_plan": (i, [i, i, i, i, vp, vp, vp]),
+    "rdb_tuning_table_load": (i, [C.c_char_p]),
+    "rdb_tuning_table_set_skinny": (i, [i, i, i, i, i, i]),
+    "rdb_tuning_table_set_dense": (i, [i, i, i, i, i]),
+    "rdb_tuning_table_clear": (i, []),
+    "rdb_tuning_table_size": (i, []),
     "rdb_skinny_gemm_max_clusters": (i, [i, i, i]),
     "rdb_skinny_gemm_trace": (i, [vp, i, i]),
     "rdb_skinny_gemm_fp8_grouped": (i, [vp, i, vp]),

@@ -501,6 +501,7 @@ static int run(const uint8_t* A, const uint8_t* B, const float* sa, const float*
     int err = 0;
     DeviceInfo* info = device_info(&err);
     if (!info) return err;
+    if (tile_rows == 0 && max_ctas == 0) lookup_dense_plan(M, N, K, &tile_rows, &max_ctas);   // a measured entry, if any
     // 256 x 256 tiles when padding M up to a multiple of 256 wastes no more than ~12 % of the work:
     // computed by CTA pairs (K a multiple of 128 bytes; a pair uses the same two SMs as two 128-row
     // tiles would, with half the B traffic), else by single CTAs when there is at least one tile

@@ -38,6 +38,11 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, 
                  uint64_t cols, uint64_t pitch_bytes, uint32_t box_cols, uint32_t box_rows, CUtensorMapSwizzle swizzle,
                  CUtensorMapL2promotion promo = CU_TENSOR_MAP_L2_PROMOTION_L2_256B);
 
+// Tuning-table lookups (tuning_table.cu): measured best configurations per shape, consulted by the
+// launchers when the caller gives no knobs.  Return false when the shape has no entry.
+bool lookup_skinny_plan(int mpad, int N, int K, int* rows, int* split_k, int* stages);
+bool lookup_dense_plan(int M, int N, int K, int* tile_rows, int* max_ctas);
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // The device word holding the wait budget exists once per translation unit

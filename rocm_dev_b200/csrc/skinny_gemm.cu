@@ -503,6 +503,8 @@ static int run(const uint8_t* A, const uint8_t* B, const float* sa, const float*
         if (maxc[c] <= 0) maxc[c] = kDefaultMaxClusters[c] * info->sm_count / 148;
         if (maxc[c] < 1) maxc[c] = 1;
     }
+    // no knobs from the caller: a measured entry of the tuning table goes before the cost model
+    if (rows_hint == 0 && split_k_hint == 0 && stages_hint == 0) lookup_skinny_plan(mpad, N, K, &rows_hint, &split_k_hint, &stages_hint);
     const Plan pl = make_plan(M, N, K, maxc, split_k_hint, stages_hint, rows_hint);
     CUtensorMap tmW, tmA;
     int r = make_tmap_2d(&tmW, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K, ldb, BK, pl.R, CU_TENSOR_MAP_SWIZZLE_128B);
@@ -638,7 +640,9 @@ int rdb_skinny_gemm_plan(int M, int N, int K, int sm_count, int* rows_per_tile, 
         maxc[c] = rdb::skinny::kDefaultMaxClusters[c] * sm_count / 148;
         if (maxc[c] < 1) maxc[c] = 1;
     }
-    const rdb::skinny::Plan pl = rdb::skinny::make_plan(M, N, K, maxc, 0, 0, 0);
+    int rows_hint = 0, split_hint = 0, stages_hint = 0;
+    rdb::lookup_skinny_plan(M <= 16 ? 16 : 32, N, K, &rows_hint, &split_hint, &stages_hint);     // a tuned entry wins
+    const rdb::skinny::Plan pl = rdb::skinny::make_plan(M, N, K, maxc, split_hint, stages_hint, rows_hint);
     if (rows_per_tile) *rows_per_tile = pl.R;
     if (split_k) *split_k = pl.split_k;
     if (stages) *stages = pl.stages;

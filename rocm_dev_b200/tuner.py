@@ -8,7 +8,14 @@ device-side wait is bounded, and a candidate is one CUDA-graph timing.  Results
 are appended to a JSON-lines file so that an interrupted search can be resumed
 (``--restart N`` skips the first N candidates, as grid.py:72-73 does).
 
-    python -m rocm_dev_b200.tuner -a "8 4096 4096" [-s] [-r N] [-o results.jsonl]
+    python -m rocm_dev_b200.tuner -a "8 4096 4096" [-s] [-r N] [-o results.jsonl] [--table tuned.txt]
+    python -m rocm_dev_b200.tuner -p dense -a "4096 4096 4096" --table tuned.txt
+
+With ``--table`` the winner is written into a tuning-table file (one line per
+shape, rewritten in place) when it beats the automatic plan; the launchers
+load that file through ``rdb_tuning_table_load`` or the environment variable
+``RDB_TUNING_TABLE`` - the counterpart of the reference compiling the chosen
+``#define``s in (grid.py:106-116).
 """
 from __future__ import annotations
 
@@ -98,14 +105,89 @@ def time_config(M, N, K, rows, split_k, stages, flags=1, iters=30, copies=None):
     return a.elapsed_time(b) * 1e3 / (3 * iters)
 
 
+def read_table(path: str) -> dict:
+    """{("skinny", mpad, N, K): (rows, split_k, stages), ("dense", M, N, K): (tile_rows, max_ctas)}"""
+    table = {}
+    if os.path.exists(path):
+        for line in open(path):
+            f = line.split("#")[0].split()
+            if f:
+                table[(f[0], int(f[1]), int(f[2]), int(f[3]))] = tuple(int(x) for x in f[4:])
+    return table
+
+
+def write_table(path: str, table: dict) -> None:
+    lines = ["# tuning table of rocm_dev_b200: measured best configurations, loaded with rdb_tuning_table_load",
+             "# skinny <m_bucket> <N> <K> <rows_per_tile> <split_k> <stages> | dense <M> <N> <K> <tile_rows> <max_ctas>"]
+    for key in sorted(table):
+        lines.append(" ".join(str(x) for x in (*key, *table[key])))
+    tmp = path + ".tmp"
+    with open(tmp, "w") as f:
+        f.write("\n".join(lines) + "\n")
+    os.replace(tmp, path)
+
+
+def dense_candidates(M: int, N: int, K: int, sm_count: int = 148):
+    """(tile_rows, max_ctas) pairs: the three tilings (CTA pairs need K % 128 == 0)
+    on the whole machine and on slightly fewer CTAs (a tile count that does not
+    divide by the SM count can finish sooner on a grid that divides it)."""
+    out = []
+    for tr in (2, 256, 128):
+        if tr == 2 and K % 128:
+            continue
+        rows = 128 if tr == 128 else 256
+        tiles = -(-M // rows) * -(-N // 256)
+        unit = 2 if tr == 2 else 1
+        grids = {0}
+        for waves in range(1, 9):
+            g = -(-tiles // waves)
+            g += g % unit
+            if sm_count // 2 <= g < sm_count:
+                grids.add(g)
+        out += [(tr, g) for g in sorted(grids)]
+    return out
+
+
+def time_dense(M, N, K, tile_rows, max_ctas, iters=10):
+    import torch
+
+    from . import dense_gemm_fp8
+    from ._lib import lib
+    dev = torch.device("cuda")
+    A = torch.randint(0, 0x78, (M, K), dtype=torch.uint8, device=dev)
+    B = torch.randint(0, 0x78, (N, K), dtype=torch.uint8, device=dev)
+    D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+    one = torch.ones(1, device=dev)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(2):
+            dense_gemm_fp8(A, B, one, one, out=D, tile_rows=tile_rows, max_ctas=max_ctas)
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record(stream)
+        for _ in range(iters):
+            dense_gemm_fp8(A, B, one, one, out=D, tile_rows=tile_rows, max_ctas=max_ctas)
+        b.record(stream)
+        torch.cuda.synchronize()
+    if lib().rdb_device_status() != 0:
+        raise RuntimeError("device-side wait timed out")
+    return a.elapsed_time(b) * 1e3 / iters
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser()
+    ap.add_argument("--project", "-p", default="skinny_gemm", choices=["skinny_gemm", "dense"])
+    ap.add_argument("--table", default="", help="tuning-table file to update with the winner")
     ap.add_argument("--arguments", "-a", required=True, help='"m n k"')
     ap.add_argument("--restart", "-r", type=int, default=0, help="skip the first N candidates")
     ap.add_argument("--shuffle", "-s", action="store_true")
     ap.add_argument("--output", "-o", default="")
     a = ap.parse_args(argv)
     M, N, K = (int(x) for x in a.arguments.split())
+    if a.project == "dense":
+        return main_dense(a, M, N, K)
+    from ._lib import lib
+    lib().rdb_tuning_table_clear()           # time the analytic plan, not an earlier table entry
     cands = candidates(M, N, K)
     if a.shuffle:
         import random
@@ -133,6 +215,44 @@ def main(argv=None):
     summary = {"shape": [M, N, K], "candidates": len(cands), "best": best, "automatic_plan": list(auto),
                "automatic_us": auto_us, "best_gbs": by / best["us"] / 1e3 if best else None,
                "automatic_gbs": by / auto_us / 1e3, "results": os.path.abspath(out_path)}
+    if a.table and best and best["us"] < auto_us:
+        table = read_table(a.table)
+        table[("skinny", 16 if M <= 16 else 32, N, K)] = (best["rows"], best["split_k"], best["stages"])
+        write_table(a.table, table)
+        summary["table"] = os.path.abspath(a.table)
+    print(json.dumps(summary))
+    return summary
+
+
+def main_dense(a, M, N, K):
+    from ._lib import lib
+    lib().rdb_tuning_table_clear()
+    out_path = a.output or f"tune_dense_{M}_{N}_{K}.jsonl"
+    best = None
+    cands = dense_candidates(M, N, K)
+    for idx, (tr, mc) in enumerate(cands):
+        if idx < a.restart:
+            continue
+        try:
+            us, err = time_dense(M, N, K, tr, mc), None
+        except Exception as e:  # noqa: BLE001  (a refused configuration reports an error instead of hanging)
+            us, err = None, str(e)
+        rec = {"index": idx, "tile_rows": tr, "max_ctas": mc, "us": us}
+        if err:
+            rec["error"] = err
+        with open(out_path, "a") as f:
+            f.write(json.dumps(rec) + "\n")
+        if us is not None and (best is None or us < best["us"]):
+            best = rec
+    auto_us = time_dense(M, N, K, 0, 0)
+    summary = {"project": "dense", "shape": [M, N, K], "candidates": len(cands), "best": best, "automatic_us": auto_us,
+               "best_tflops": 2.0 * M * N * K / best["us"] / 1e6 if best else None,
+               "automatic_tflops": 2.0 * M * N * K / auto_us / 1e6, "results": os.path.abspath(out_path)}
+    if a.table and best and best["us"] < auto_us:
+        table = read_table(a.table)
+        table[("dense", M, N, K)] = (best["tile_rows"], best["max_ctas"])
+        write_table(a.table, table)
+        summary["table"] = os.path.abspath(a.table)
     print(json.dumps(summary))
     return summary
 
