@@ -354,6 +354,28 @@ int rdb_ar_set_trace(void *ctx, unsigned long long *device_buffer16);
 int rdb_ar_allreduce(void *ctx, const uint16_t *x, uint16_t *out, size_t n, int algo, void *stream);
 const uint16_t *rdb_ar_result(void *ctx);
 
+/* Row-parallel linear layer + allreduce in two launches instead of three and
+ * without the bf16 intermediate in HBM: every rank multiplies its K slice,
+ *   P_r[M,N] = bf16((A_r . B_r^T) * scale_a * scale_b)     (the problem, as for rdb_skinny_gemm_fp8_grouped),
+ * and out = the FP8-encoded allreduce of the P_r as defined above (flattened
+ * [M*N], blocks of 128 along N), identical bits on every rank.  The GEMM
+ * epilogue quantises its result and stores codes and scales straight into
+ * every rank's staging slots - the allreduce's "read x, encode, push" step and
+ * the round trip of P_r through HBM disappear; the second launch waits for all
+ * ranks, decodes, sums in rank order and writes `out` (M*N bf16).  problem->D
+ * is not written (may be NULL).  Requires N % 128 == 0 and M*N <= 2^20 (the
+ * one-shot limit) and <= the context's max_elems.  The result equals
+ * rdb_ar_allreduce (one-shot) applied to the D that
+ * rdb_skinny_gemm_fp8_grouped(problem, 1) writes, bit for bit.  Collective:
+ * every rank calls it with the same M and N.  No reference counterpart (the
+ * reference has neither collective nor fused epilogue); the epilogue it
+ * replaces is projects/skinny_gemm/consumers/mfma_16x16x32_consumer.cu:111-162.
+ * _begin / _finish are the two launches one by one, for drivers that emulate
+ * several ranks on ONE GPU: _begin for every rank before _finish for any. */
+int rdb_skinny_gemm_fp8_allreduce(void *ar_ctx, const rdb_skinny_problem *problem, uint16_t *out, void *stream);
+int rdb_skinny_gemm_fp8_allreduce_begin(void *ar_ctx, const rdb_skinny_problem *problem, void *stream);
+int rdb_skinny_gemm_fp8_allreduce_finish(void *ar_ctx, uint16_t *out, void *stream);
+
 /* The three launches of a call one by one (phase 1 push, 2 reduce, 3 gather),
  * all with the epoch rdb_ar_begin_call returned.  For drivers that emulate
  * several ranks on ONE GPU: issue phase p for every rank before phase p+1 for

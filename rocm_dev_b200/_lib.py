@@ -64,6 +64,9 @@ _SIGNATURES = {
     "rdb_ar_register_buffers": (i, [vp, C.POINTER(C.c_void_p), C.c_size_t]),
     "rdb_ar_allreduce": (i, [vp, vp, vp, C.c_size_t, i, vp]),
     "rdb_ar_result": (C.c_void_p, [vp]),
+    "rdb_skinny_gemm_fp8_allreduce": (i, [vp, vp, vp, vp]),
+    "rdb_skinny_gemm_fp8_allreduce_begin": (i, [vp, vp, vp]),
+    "rdb_skinny_gemm_fp8_allreduce_finish": (i, [vp, vp, vp]),
     "rdb_ar_begin_call": (i, [vp]),
     "rdb_ar_phase": (i, [vp, i, i, vp, vp, C.c_size_t, i, vp]),
     "rdb_debug_division_mismatches": (i, [vp, i, vp, vp]),

@@ -216,6 +216,26 @@ class Fp8AllReduce:
                 check(lib().rdb_device_status(), "rdb_ar_allreduce (device status)")
         return out
 
+    def skinny_gemm_all_reduce(self, A: torch.Tensor, B: torch.Tensor, scale_a: torch.Tensor, scale_b: torch.Tensor,
+                               out: torch.Tensor | None = None) -> torch.Tensor:
+        """Row-parallel linear + allreduce (rdb_skinny_gemm_fp8_allreduce): this
+        rank's K slice ``A [M,K_r]``, ``B [N,K_r]`` is multiplied and the bf16
+        partial product goes, block-quantised by the GEMM's epilogue, straight
+        into every rank's staging area; the result ``[M,N]`` bf16 is the
+        FP8-encoded allreduce of the ranks' partial products.  N % 128 == 0,
+        M * N <= 2**20."""
+        from .skinny_gemm import _problem_array
+        M, N = A.shape[0], B.shape[0]
+        if out is None:
+            out = torch.empty((M, N), dtype=torch.bfloat16, device=self.device)
+        assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.numel() == M * N
+        arr = _problem_array([(A, B, scale_a, scale_b, out)])      # D of the problem is not written by the fused call
+        with torch.cuda.device(self.device):
+            check(lib().rdb_skinny_gemm_fp8_allreduce(self.ctx, arr, out.data_ptr(),
+                                                      torch.cuda.current_stream(self.device).cuda_stream),
+                  "rdb_skinny_gemm_fp8_allreduce")
+        return out
+
     def all_reduce_in_workspace(self, x: torch.Tensor) -> torch.Tensor:
         """Two-shot allreduce whose result is left in the workspace: returns a
         bf16 view of it (no copy-out), valid until this rank's next call."""
@@ -279,6 +299,22 @@ class LocalRanks:
                 for r in range(self.world):
                     check(lib().rdb_ar_phase(self.ctx[r], phase, epoch, xs[r].data_ptr(), outs[r].data_ptr(), n, algo,
                                              stream), "rdb_ar_phase")
+        return outs
+
+    def skinny_gemm_all_reduce(self, operands):
+        """operands: per emulated rank (A_r, B_r, scale_a, scale_b).  The
+        producer launches of all ranks first, then the consuming ones."""
+        from .skinny_gemm import _problem_array
+        M, N = operands[0][0].shape[0], operands[0][1].shape[0]
+        outs = [torch.empty((M, N), dtype=torch.bfloat16, device=self.device) for _ in operands]
+        stream = torch.cuda.current_stream(self.device).cuda_stream
+        with torch.cuda.device(self.device):
+            for r, (A, B, sa, sb) in enumerate(operands):
+                check(lib().rdb_skinny_gemm_fp8_allreduce_begin(self.ctx[r], _problem_array([(A, B, sa, sb, outs[r])]), stream),
+                      "rdb_skinny_gemm_fp8_allreduce_begin")
+            for r in range(self.world):
+                check(lib().rdb_skinny_gemm_fp8_allreduce_finish(self.ctx[r], outs[r].data_ptr(), stream),
+                      "rdb_skinny_gemm_fp8_allreduce_finish")
         return outs
 
     def close(self):

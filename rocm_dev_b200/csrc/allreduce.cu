@@ -47,6 +47,7 @@
 #include <cstdlib>
 #include <cstring>
 
+#include "ar_internal.h"
 #include "fp8_codec.cuh"
 #include "host_util.h"
 #include "ptx.cuh"
@@ -101,6 +102,8 @@ struct Ctx {
     unsigned epoch;
     int push_order;       // 0 linear, 1 rotated by rank, 2 owner-interleaved (default)
     unsigned long long* trace;   // optional: 8 globaltimer stamps of the last fused call (diagnostics)
+    size_t pending_n;     // a call opened by begin_prepushed and not yet finished (0: none)
+    unsigned pending_epoch;
 };
 
 struct KParams {
@@ -681,6 +684,43 @@ static int check_call(Ctx* c, const uint16_t* x, uint16_t* out, size_t n, int& a
     return RDB_SUCCESS;
 }
 
+int begin_prepushed(void* ctx, size_t n, PushTarget* t) {
+    Ctx* c = static_cast<Ctx*>(ctx);
+    if (!c || !t) return RDB_INVALID_CONFIG;
+    if (n == 0 || n % 128 != 0) return RDB_BAD_SHAPE;
+    if (n > c->max_elems || n > kOneShotMaxElems) return RDB_SIZE_ABOVE_LIMIT;
+    if (c->pending_n != 0) return RDB_INVALID_CONFIG;          // one open call at a time
+    for (int i = 0; i < 8; i++) t->ws[i] = i < c->world ? c->ws[i] : nullptr;
+    t->off_q = c->L.off_q;
+    t->off_s = c->L.off_s;
+    t->off_flags = c->L.off_flags;
+    t->slot_groups = c->L.slot_groups;
+    t->rank = c->rank;
+    t->world = c->world;
+    t->epoch = ++c->epoch;
+    c->pending_n = n;
+    c->pending_epoch = t->epoch;
+    return RDB_SUCCESS;
+}
+
+void cancel_prepushed(void* ctx) {
+    Ctx* c = static_cast<Ctx*>(ctx);
+    if (c && c->pending_n != 0) {
+        c->pending_n = 0;
+        c->epoch--;
+    }
+}
+
+int finish_prepushed(void* ctx, uint16_t* out, cudaStream_t stream) {
+    Ctx* c = static_cast<Ctx*>(ctx);
+    if (!c || c->pending_n == 0) return RDB_INVALID_CONFIG;
+    if (!out || !aligned16(out)) return RDB_BAD_ALIGNMENT;
+    const size_t n = c->pending_n;
+    c->pending_n = 0;
+    // phase 2 of a one-shot call: the reduce kernel waits for every rank's "pushed" flag and writes `out`
+    return run_phase(c, 2, nullptr, out, n, 1, c->pending_epoch, stream);
+}
+
 }  // namespace ar
 }  // namespace rdb
 
@@ -728,6 +768,8 @@ int rdb_ar_create(int rank, int world, void* const* workspaces, size_t max_elems
     for (int i = 0; i < rdb::ar::kMaxWorld; i++) c->reg[i] = nullptr;
     c->reg_bytes = 0;
     c->epoch = 0;
+    c->pending_n = 0;
+    c->pending_epoch = 0;
     c->trace = nullptr;
     // The epoch restarts at zero, so flag words left by an earlier context over the same workspace must
     // go: this rank's flag block is cleared here.  Creation is a collective set-up step - no rank may
@@ -785,6 +827,7 @@ int rdb_ar_allreduce(void* ctx, const uint16_t* x, uint16_t* out, size_t n, int 
     Ctx* c = static_cast<Ctx*>(ctx);
     int r = check_call(c, x, out, n, algo);
     if (r != RDB_SUCCESS) return r;
+    if (c->pending_n != 0) return RDB_INVALID_CONFIG;    // a fused GEMM + allreduce call is still open on this context
     // Cutting large messages into chunks on two internal streams (encoder of
     // chunk i+1 over the all-gather of chunk i) was measured slower than one
     // call (187 vs 157 us at 64 MiB on two GPUs): not done.

@@ -41,8 +41,12 @@
 #include <cstring>
 #include <mutex>
 
+#include "ar_internal.h"
+#include "fp8_codec.cuh"
 #include "host_util.h"
 #include "ptx.cuh"
+
+#include <cuda_fp8.h>
 
 RDB_DEFINE_WAIT_BUDGET_SETTER()
 
@@ -74,9 +78,11 @@ struct Params {
     int range_begin[kMaxCtas + 1];          // CTA c works on units [range_begin[c], range_begin[c + 1])
     int count;
     float* partial;                         // [grid][32][256] fp32
-    unsigned* words;                        // [0]: launch epoch, [1]: CTAs that finished, [8 + 2 c + e]: partial flags
+    unsigned* words;                        // [0]: launch epoch, [1]: CTAs that finished, [2]: a CTA gave up (fused
+                                            // delivery), [8 + 2 c + e]: partial flags
     int* status;
     unsigned long long* trace;              // optional [grid][4] %globaltimer stamps, else nullptr
+    rdb::ar::PushTarget push;               // world > 0: the result goes, block-quantised, to the allreduce staging
 };
 
 __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
@@ -119,6 +125,48 @@ __device__ __forceinline__ void store_chunk(const Problem& pr, const float* v, f
         for (int j = 0; j < 32; j++)            // fully unrolled: v stays in registers
             if (j < valid && n + j < pr.N) out[j] = __float2bfloat16_rn(v[j] * sc);
     }
+}
+
+// GEMM -> allreduce fusion: one finished 128-column block of output row m (bf16
+// values packed two per word, their maximum magnitude in `amax`) is encoded
+// exactly like the allreduce's own encoder does - scale amax/448, e4m3 codes of
+// x / scale - and stored into every rank's staging slot for flattened element
+// `elem` of the [M,N] result.
+__device__ __forceinline__ void push_block128(const rdb::ar::PushTarget& t, const uint32_t* packed, float amax, size_t elem) {
+    const float s = rdb::ar::block_scale(amax);
+    rdb::ar::BlockDivisor d;
+    d.set(s);
+    const size_t g = elem / 512;
+    const int blk = static_cast<int>((elem % 512) / 128);
+    const size_t slot = (static_cast<size_t>(t.epoch & 1u) * t.world + t.rank) * t.slot_groups + g;
+#pragma unroll 1
+    for (int i = 0; i < 8; i++) {                       // 16 elements -> 16 code bytes per step
+        uint32_t q[4];
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            float x[8], y[8];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint32_t w = packed[8 * i + 4 * h + j];
+                x[2 * j] = __uint_as_float(w << 16);
+                x[2 * j + 1] = __uint_as_float(w & 0xFFFF0000u);
+            }
+            d.div8(x, y);
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const __nv_fp8x2_storage_t a = __nv_cvt_float2_to_fp8x2(make_float2(y[4 * j], y[4 * j + 1]), __NV_SATFINITE, __NV_E4M3);
+                const __nv_fp8x2_storage_t b = __nv_cvt_float2_to_fp8x2(make_float2(y[4 * j + 2], y[4 * j + 3]), __NV_SATFINITE, __NV_E4M3);
+                q[2 * h + j] = static_cast<uint32_t>(a) | (static_cast<uint32_t>(b) << 16);
+            }
+        }
+        for (int k = 0; k < t.world; k++) {
+            int peer = t.rank + 1 + k;
+            if (peer >= t.world) peer -= t.world;
+            reinterpret_cast<uint4*>(t.ws[peer] + t.off_q + slot * 512 + blk * 128)[i] = make_uint4(q[0], q[1], q[2], q[3]);
+        }
+    }
+    for (int k = 0; k < t.world; k++)
+        reinterpret_cast<float*>(t.ws[k] + t.off_s)[slot * 4 + blk] = s;
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __grid_constant__ Params p) {
@@ -271,6 +319,38 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
                     }
                 }
                 if (!live) { *abort_flag = 1; if (lane == 0) report_timeout(p.status); }
+                if (p.push.world > 0) {
+                    // fused delivery: warp e takes whole 128-column blocks (R is a multiple of 128 here), keeps the
+                    // block's bf16 values packed in registers and hands them to the encoder
+                    for (int b0 = 128 * e; b0 < pr.R && n0 + b0 < pr.N; b0 += 256) {
+                        uint32_t packed[64];
+                        float amax = 0.0f;
+#pragma unroll
+                        for (int c = 0; c < 4; c++) {
+                            float v[32];
+                            tmem_ld32(taddr + b0 + 32 * c, v);
+                            if (lane < pr.M && live) {
+                                for (int j = cta + 1; j <= last_partner; j++) {
+                                    if (p.range_begin[j] == p.range_begin[j + 1]) continue;
+                                    const float4* src = reinterpret_cast<const float4*>(p.partial + static_cast<size_t>(j) * SLOT_FLOATS + lane * MAX_R + b0 + 32 * c);
+#pragma unroll
+                                    for (int q = 0; q < 8; q++) {
+                                        const float4 t = __ldcg(src + q);
+                                        v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
+                                    }
+                                }
+                            }
+#pragma unroll
+                            for (int j = 0; j < 16; j++) {
+                                const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * j] * sc, v[2 * j + 1] * sc);
+                                const uint32_t w = *reinterpret_cast<const uint32_t*>(&h2);
+                                packed[16 * c + j] = w;
+                                amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w << 16)), fabsf(__uint_as_float(w & 0xFFFF0000u))));
+                            }
+                        }
+                        if (lane < pr.M && live) push_block128(p.push, packed, amax, static_cast<size_t>(lane) * pr.N + n0 + b0);
+                    }
+                } else
                 for (int c0 = 32 * e; c0 < pr.R; c0 += 64) {
                     float v[32];
                     tmem_ld32(taddr + c0, v);
@@ -308,12 +388,23 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
         stamp(p, 3);
         // the last CTA to finish opens the next launch's epoch (partial flags are compared with it, so
         // nothing is ever reset and a replayed CUDA graph behaves like a fresh launch)
-        __threadfence();
+        if (p.push.world > 0 && *abort_flag != 0) atomicOr(p.words + 2, 1u);   // a wait of this CTA ran out
+        if (p.push.world > 0) __threadfence_system(); else __threadfence();   // fused: this CTA's peer stores are out
         const unsigned done = atomicAdd(p.words + 1, 1u);
         if (done == gridDim.x - 1) {
             p.words[1] = 0;
             __threadfence();
             atomicAdd(p.words, 1u);
+            if (p.push.world > 0) {
+                // every CTA has delivered and fenced: tell all ranks that this rank's blocks of the call are in
+                // place (the allreduce's "pushed" flag of this epoch; a wait that ran out here marks it failed)
+                __threadfence_system();
+                const unsigned word = (p.push.epoch << 1) | (atomicExch(p.words + 2, 0u) & 1u);
+                for (int k = 0; k < p.push.world; k++) {
+                    unsigned* f = reinterpret_cast<unsigned*>(p.push.ws[k] + p.push.off_flags) + (p.push.epoch & 1u) * 8 + p.push.rank;
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(word) : "memory");
+                }
+            }
         }
     }
 }
@@ -392,8 +483,11 @@ static void plan(const rdb_skinny_problem* pr, int count, int grid, int* R_out, 
     range_begin[grid] = total_units;
 }
 
-static int run(const rdb_skinny_problem* pr, int count, cudaStream_t stream) {
+// `push`: nullptr for a plain grouped GEMM; else the one problem's result is delivered, block-quantised, to the
+// allreduce staging it describes (D is not written).
+static int run(const rdb_skinny_problem* pr, int count, cudaStream_t stream, const rdb::ar::PushTarget* push = nullptr) {
     if (!pr || count < 1 || count > kMaxProblems) return RDB_INVALID_CONFIG;
+    if (push && (count != 1 || pr[0].N % 128 != 0)) return RDB_INVALID_CONFIG;
     long long units = 0;
     for (int i = 0; i < count; i++) {
         const rdb_skinny_problem& q = pr[i];
@@ -402,6 +496,7 @@ static int run(const rdb_skinny_problem* pr, int count, cudaStream_t stream) {
         if (q.N % 2 != 0) return RDB_N_NOT_EVEN;
         if (q.K % 16 != 0 || q.ldb % 16 != 0) return RDB_K_NOT_DIVISIBLE_BY_WARPTILE_K;
         if (!aligned16(q.A) || !aligned16(q.B) || (reinterpret_cast<uintptr_t>(q.D) & 1u)) return RDB_BAD_ALIGNMENT;
+        if (!push && !q.D) return RDB_INVALID_CONFIG;
         if (!q.scale_a || !q.scale_b) return RDB_INVALID_CONFIG;
         units += static_cast<long long>((q.N + 15) / 16) * ((q.K + BK - 1) / BK);
     }
@@ -442,6 +537,8 @@ static int run(const rdb_skinny_problem* pr, int count, cudaStream_t stream) {
     prm.words = ws->words;
     prm.status = info->status_dev;
     prm.trace = g_trace;
+    if (push) prm.push = *push;
+    else memset(&prm.push, 0, sizeof(prm.push));
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(grid, 1, 1);
@@ -467,6 +564,28 @@ extern "C" {
 
 int rdb_skinny_gemm_fp8_grouped(const rdb_skinny_problem* problems, int count, void* stream) {
     return rdb::grouped::run(problems, count, static_cast<cudaStream_t>(stream));
+}
+
+int rdb_skinny_gemm_fp8_allreduce_begin(void* ar_ctx, const rdb_skinny_problem* problem, void* stream) {
+    if (!ar_ctx || !problem) return RDB_INVALID_CONFIG;
+    if (problem->M < 1 || problem->N < 1) return RDB_BAD_SHAPE;
+    if (problem->N % 128 != 0) return RDB_BAD_SHAPE;
+    rdb::ar::PushTarget t;
+    int r = rdb::ar::begin_prepushed(ar_ctx, static_cast<size_t>(problem->M) * problem->N, &t);
+    if (r != RDB_SUCCESS) return r;
+    r = rdb::grouped::run(problem, 1, static_cast<cudaStream_t>(stream), &t);
+    if (r != RDB_SUCCESS) rdb::ar::cancel_prepushed(ar_ctx);     // nothing was launched: the ranks' epochs stay in step
+    return r;
+}
+
+int rdb_skinny_gemm_fp8_allreduce_finish(void* ar_ctx, uint16_t* out, void* stream) {
+    return rdb::ar::finish_prepushed(ar_ctx, out, static_cast<cudaStream_t>(stream));
+}
+
+int rdb_skinny_gemm_fp8_allreduce(void* ar_ctx, const rdb_skinny_problem* problem, uint16_t* out, void* stream) {
+    if (!out || !rdb::aligned16(out)) return RDB_BAD_ALIGNMENT;
+    const int r = rdb_skinny_gemm_fp8_allreduce_begin(ar_ctx, problem, stream);
+    return r != RDB_SUCCESS ? r : rdb_skinny_gemm_fp8_allreduce_finish(ar_ctx, out, stream);
 }
 
 int rdb_skinny_gemm_grouped_plan(const rdb_skinny_problem* problems, int count, int ctas, int* rows_per_unit,

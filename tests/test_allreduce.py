@@ -292,6 +292,75 @@ def test_emulated_ranks_deliver_into_registered_buffers(cuda_device, oracle, wor
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("M,N,K", [(8, 4096, 4096), (16, 1024, 2048), (3, 384, 512), (32, 6144, 1024), (1, 128, 128)])
+def test_gemm_epilogue_feeds_the_allreduce(cuda_device, oracle, world, M, N, K):
+    """Row-parallel linear + allreduce with the fused epilogue: K is split over
+    the (emulated) ranks, each rank's GEMM quantises its bf16 partial product
+    and delivers it to every rank's staging area, the consuming launch reduces.
+    Bit-exact against the oracle's allreduce of the partial products that the
+    plain grouped GEMM writes for the same slices - which in turn meet the GEMM
+    tolerance against the oracle's GEMM."""
+    import rocm_dev_b200 as R
+    from rocm_dev_b200 import quant
+    from helpers import bf16_bits, check_gemm_parity
+    if K % (128 * world) != 0:
+        pytest.skip("K slice must stay a multiple of 128 bytes")
+    dev = cuda_device
+    Aq, Bq, sa, sb = quant.synthetic_gemm_operands(M, N, K, seed=world + M)
+    kr = K // world
+    ops = [(Aq[:, r * kr:(r + 1) * kr].contiguous().to(dev), Bq[:, r * kr:(r + 1) * kr].contiguous().to(dev), sa.to(dev), sb.to(dev))
+           for r in range(world)]
+    lr = R.LocalRanks(world, max_elems=1 << 20, device=dev)
+    try:
+        for rep in range(2):                                  # both staging sets
+            outs = lr.skinny_gemm_all_reduce(ops)
+            torch.cuda.synchronize()
+            assert R.lib().rdb_device_status() == 0
+            partial = []
+            for r, (A, B, a, b) in enumerate(ops):            # the unfused composition, same kernels
+                D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+                assert R.skinny_gemm_fp8_grouped([(A, B, a, b, D)]) == 0
+                partial.append(D)
+                ref = oracle.gemm_fp8_bf16(A.cpu().numpy(), B.cpu().numpy(), sa.item(), sb.item())
+                ref64, mag = oracle.gemm_fp8_f64(A.cpu().numpy(), B.cpu().numpy(), sa.item(), sb.item())
+                check_gemm_parity(bf16_bits(D), ref, ref64, mag, kr)
+            want, _, _ = oracle.allreduce_fp8(np.stack([_bits(p.reshape(-1)) for p in partial]))
+            for r in range(world):
+                assert np.array_equal(_bits(outs[r].reshape(-1)), want), (world, M, N, K, rep, r)
+            # an ordinary call on the same contexts afterwards (epochs and staging sets stay in step)
+            xs = [torch.randn(1024, generator=torch.Generator().manual_seed(r)).bfloat16().to(dev) for r in range(world)]
+            got = lr.all_reduce(xs, algo=1)
+            w2, _, _ = oracle.allreduce_fp8(np.stack([_bits(x) for x in xs]))
+            assert np.array_equal(_bits(got[0]), w2)
+    finally:
+        lr.close()
+
+
+@pytest.mark.gpu
+def test_fused_linear_rejects_what_it_cannot_do(cuda_device):
+    import rocm_dev_b200 as R
+    from rocm_dev_b200.skinny_gemm import SkinnyProblem
+    import ctypes as C
+    L = R.lib()
+    lr = R.LocalRanks(1, max_elems=4096, device=cuda_device)
+    try:
+        x = torch.zeros(1 << 16, dtype=torch.uint8, device=cuda_device)
+        f = torch.ones(1, device=cuda_device)
+        pr = lambda M, N, K: SkinnyProblem(x.data_ptr(), x.data_ptr(), f.data_ptr(), f.data_ptr(), None, M, N, K, K)  # noqa: E731
+        assert L.rdb_skinny_gemm_fp8_allreduce_begin(lr.ctx[0], C.byref(pr(8, 192, 128)), 0) == 8      # N % 128
+        assert L.rdb_skinny_gemm_fp8_allreduce_begin(lr.ctx[0], C.byref(pr(32, 256, 128)), 0) == 11    # above max_elems
+        assert L.rdb_skinny_gemm_fp8_allreduce_finish(lr.ctx[0], x.data_ptr(), 0) == 6                 # nothing open
+        assert L.rdb_skinny_gemm_fp8_allreduce_begin(lr.ctx[0], C.byref(pr(8, 128, 40)), 0) == 3       # refused by the GEMM ...
+        out = torch.empty(8 * 128, dtype=torch.bfloat16, device=cuda_device)
+        assert L.rdb_ar_allreduce(lr.ctx[0], out.data_ptr(), out.data_ptr(), 1024, 1, 0) == 0          # ... and the epoch was given back
+        torch.cuda.synchronize()
+        assert L.rdb_device_status() == 0
+    finally:
+        lr.close()
+
+
+@pytest.mark.gpu
 def test_a_wait_that_runs_out_is_reported_and_leaves_everything_usable(cuda_device, oracle):
     """Failure detection without a fault: with a 2 ms wait budget, rank 0's
     reduce step is issued while rank 1's encoded blocks are withheld by the
