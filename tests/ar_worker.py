@@ -62,6 +62,26 @@ def main():
             got = out.cpu().view(torch.int16).numpy().view(np.uint16)
             assert np.array_equal(got, want), f"rank {rank} registered n {n} rep {rep}: {(got != want).sum()} differ"
             dist.barrier()               # nobody starts the next call while a rank still reads this result
+    # row-parallel linear + allreduce with the GEMM epilogue feeding the staging area: K split over the ranks
+    from rocm_dev_b200 import quant
+    for (M, N, K) in ((8, 4096, 4096), (16, 1024, 2048 * world), (32, 6144, 1024 * world)):
+        Aq, Bq, sa, sb = quant.synthetic_gemm_operands(M, N, K, seed=world + M)
+        kr = K // world
+        sl = [(Aq[:, r * kr:(r + 1) * kr].contiguous().to(dev), Bq[:, r * kr:(r + 1) * kr].contiguous().to(dev)) for r in range(world)]
+        dsa, dsb = sa.to(dev), sb.to(dev)
+        partial = []
+        for r in range(world):                           # every rank's partial product, computed here with the same kernel
+            D = torch.empty((M, N), dtype=torch.bfloat16, device=dev)
+            assert R.skinny_gemm_fp8_grouped([(sl[r][0], sl[r][1], dsa, dsb, D)]) == 0
+            partial.append(D.reshape(-1).cpu().view(torch.int16).numpy().view(np.uint16))
+        want = O.allreduce_fp8(np.stack(partial))[0]
+        for rep in range(2):
+            out = ar.skinny_gemm_all_reduce(sl[rank][0], sl[rank][1], dsa, dsb)
+            torch.cuda.synchronize()
+            assert R.lib().rdb_device_status() == 0, "device-side wait timed out"
+            got = out.reshape(-1).cpu().view(torch.int16).numpy().view(np.uint16)
+            assert np.array_equal(got, want), f"rank {rank} fused linear {M}x{N}x{K} rep {rep}: {(got != want).sum()} differ"
+            dist.barrier()
     dist.barrier()
     ar.close()
     dist.destroy_process_group()
