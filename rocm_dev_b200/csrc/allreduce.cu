@@ -552,9 +552,11 @@ __global__ void __launch_bounds__(kThreads) quantize_blocks128_kernel(const __nv
     const int lane = threadIdx.x & 31;
     const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
     const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
+    // the loads of the next group are in flight while this one is encoded (the encoder is latency-bound)
+    uint4 in[2], in_next[2];
+    if (warp < groups) load_group(x, n, warp, lane, in);
     for (size_t g = warp; g < groups; g += nwarps) {
-        uint4 in[2];
-        load_group(x, n, g, lane, in);
+        if (g + nwarps < groups) load_group(x, n, g + nwarps, lane, in_next);
 #pragma unroll
         for (int h = 0; h < 2; h++) {
             const size_t e0 = g * kGroup + 256 * h + static_cast<size_t>(lane) * 8;
@@ -565,6 +567,8 @@ __global__ void __launch_bounds__(kThreads) quantize_blocks128_kernel(const __nv
                 if ((lane & 15) == 0) scales[e0 / 128] = s;
             }
         }
+        in[0] = in_next[0];
+        in[1] = in_next[1];
     }
 }
 

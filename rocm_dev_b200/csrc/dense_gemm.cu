@@ -252,8 +252,8 @@ dense_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant
 // four MMAs per stage the issuing thread, not the tensor pipe, set the pace.
 // Barriers: `full` lives in the even CTA and counts
 // the bytes of all four loads; `empty` and `acc_full` exist in both CTAs and are
-// signalled by one tcgen05.commit each; `acc_empty` lives in the even CTA and
-// collects the eight epilogue warps of the pair.
+// signalled in both by one tcgen05.commit with a two-CTA mask; `acc_empty`
+// lives in the even CTA and collects the eight epilogue warps of the pair.
 namespace pairk {
 constexpr int CHUNK_BYTES = 128 * BK;           // 128 rows x 128 bytes
 constexpr int PAIR_THREADS = 224;               // warp 0: A loads, 1: MMA, 2-5: epilogue, 6: B loads
@@ -347,7 +347,6 @@ dense_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
             constexpr uint32_t idesc = idesc_e4m3_f32(256, 256);
-            const uint32_t empty_odd0 = mapa_smem(empty0, 1), acc_full_odd0 = mapa_smem(acc_full0, 1);
             int it = 0, t = 0;
             bool ok = true;
             for (int tile = pair_id; tile < num_tiles && ok && *abort_flag == 0; tile += num_pairs, t++) {
@@ -368,12 +367,10 @@ dense_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                             tc_mma_f8_pair(d, smem_desc_k128(a + c * CHUNK_BYTES + ks * 32), smem_desc_k128(b + c * CHUNK_BYTES + ks * 32),
                                            idesc, (kb | c | ks) != 0);
                     }
-                    tc_commit_pair(empty0 + 8 * s);
-                    tc_commit_pair(empty_odd0 + 8 * s);
-                    if (kb == p.num_kb - 1) {
-                        tc_commit_pair(acc_full0 + 8 * acc);
-                        tc_commit_pair(acc_full_odd0 + 8 * acc);
-                    }
+                    // one commit each reaches the barrier of both CTAs: the issuing thread's time per stage, not
+                    // the tensor pipe, sets this kernel's pace, and a commit costs it about as much as two MMAs
+                    tc_commit_pair_both(empty0 + 8 * s);
+                    if (kb == p.num_kb - 1) tc_commit_pair_both(acc_full0 + 8 * acc);
                 }
             }
             if (!ok) { *abort_flag = 1; report_timeout(p.status); }

@@ -231,6 +231,13 @@ __device__ __forceinline__ void tc_commit_pair(uint32_t bar_cluster) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster)
                  : "memory");
 }
+// The same arrival delivered to the barrier at this shared-memory offset in BOTH CTAs of the pair by one
+// instruction (a commit, not a load: nothing is copied).
+__device__ __forceinline__ void tc_commit_pair_both(uint32_t bar_local) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar_local), "h"(static_cast<uint16_t>(3))
+                 : "memory");
+}
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
 }
