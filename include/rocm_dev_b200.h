@@ -126,7 +126,7 @@ int rdb_skinny_gemm_plan(int M, int N, int K, int sm_count, int *rows_per_tile, 
  * rdb_dense_gemm_fp8 / _f32 before their analytic plans.  Written by the tuner
  * (python -m rocm_dev_b200.tuner --table FILE), loaded from a text file - lines
  * "skinny <m_bucket 16|32> <N> <K> <rows_per_tile> <split_k> <stages>" and
- * "dense <M> <N> <K> <tile_rows 128|256|2> <max_ctas>", 0 = automatic for a
+ * "dense <M> <N> <K> <tile_rows 128|256|2|3> <max_ctas>", 0 = automatic for a
  * knob, '#' comments - either explicitly or, on first use, from the file the
  * environment variable RDB_TUNING_TABLE names.  Process-wide, thread-safe; a
  * later entry for the same shape replaces the earlier one; a file with a bad
@@ -208,7 +208,8 @@ int rdb_dense_gemm_fp8(const uint8_t *A, const uint8_t *B, const float *scale_a,
 
 /* Tuner entry of the dense GEMM: tile_rows selects 128 x 256 or 256 x 256 output
  * tiles computed by one CTA (128, 256), or 256 x 256 tiles computed by pairs of
- * CTAs (2; K must be a multiple of 128); 0 = automatic.  max_ctas caps the
+ * CTAs (2: two 128-byte k-blocks per pipeline stage, three stages; 3: three
+ * k-blocks per stage, two stages; K must be a multiple of 128); 0 = automatic.  max_ctas caps the
  * persistent grid (0 = one CTA per SM).  The reference fixes its tiles with #defines (projects/
  * async_gemm_16x16x64/core.cu:21-31) and retunes by recompiling (grid.py). */
 int rdb_dense_gemm_fp8_tuned(const uint8_t *A, const uint8_t *B, const float *scale_a, const float *scale_b,

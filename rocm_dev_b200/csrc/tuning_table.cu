@@ -5,7 +5,7 @@
 // (grid.py:106-116 in the reference project); here the chosen configuration is
 // a line of a text file loaded at run time:
 //   skinny <m_bucket: 16|32> <N> <K> <rows_per_tile> <split_k> <stages>
-//   dense  <M> <N> <K> <tile_rows: 128|256|2> <max_ctas>
+//   dense  <M> <N> <K> <tile_rows: 128|256|2|3> <max_ctas>
 // '#' starts a comment.  The file named by the environment variable
 // RDB_TUNING_TABLE is loaded on first use.  Host code only.
 #include <cstdio>
@@ -31,7 +31,7 @@ bool skinny_ok(int mpad, int N, int K, int rows, int sk, int st) {
            st >= 0 && st <= 16;
 }
 bool dense_ok(int M, int N, int K, int tr, int mc) {
-    return M > 0 && N > 0 && K > 0 && (tr == 0 || tr == 128 || tr == 256 || tr == 2) && mc >= 0;
+    return M > 0 && N > 0 && K > 0 && (tr == 0 || tr == 128 || tr == 256 || tr == 2 || tr == 3) && mc >= 0;
 }
 
 void put_skinny(const SkinnyEntry& e) {

@@ -132,12 +132,12 @@ def dense_candidates(M: int, N: int, K: int, sm_count: int = 148):
     on the whole machine and on slightly fewer CTAs (a tile count that does not
     divide by the SM count can finish sooner on a grid that divides it)."""
     out = []
-    for tr in (2, 256, 128):
-        if tr == 2 and K % 128:
+    for tr in (2, 3, 256, 128):
+        if tr in (2, 3) and K % 128:
             continue
         rows = 128 if tr == 128 else 256
         tiles = -(-M // rows) * -(-N // 256)
-        unit = 2 if tr == 2 else 1
+        unit = 2 if tr in (2, 3) else 1
         grids = {0}
         for waves in range(1, 9):
             g = -(-tiles // waves)

@@ -54,6 +54,20 @@ def test_both_tile_heights(cuda_device, oracle, tile_rows, M, N, K):
     check_gemm_parity(bf16_bits(out), ref, ref64, mag, K)
 
 
+@pytest.mark.parametrize("M,N,K", [(512, 512, 1024), (300, 520, 384), (1280, 768, 512), (257, 255, 128), (512, 256, 896)])
+def test_cta_pairs_with_three_k_blocks_per_stage(cuda_device, M, N, K):
+    """tile_rows = 3: same tiles, deeper stages (K not a multiple of 384 ends in a zero-filled chunk); the
+    accumulation order is unchanged, so the bits equal the two-chunk pair kernel's."""
+    import rocm_dev_b200 as R
+    Aq, Bq, sa, sb = _operands(M, N, K, seed=17)
+    dev = cuda_device
+    a = R.dense_gemm_fp8(Aq.to(dev), Bq.to(dev), sa.to(dev), sb.to(dev), tile_rows=3)
+    b = R.dense_gemm_fp8(Aq.to(dev), Bq.to(dev), sa.to(dev), sb.to(dev), tile_rows=2)
+    torch.cuda.synchronize()
+    assert R.lib().rdb_device_status() == 0
+    assert torch.equal(a, b)
+
+
 @pytest.mark.parametrize("max_ctas", [2, 0])
 @pytest.mark.parametrize("M,N,K", [(512, 512, 1024), (300, 520, 384), (1280, 768, 512), (257, 255, 128), (100, 40, 256)])
 def test_cta_pairs(cuda_device, oracle, max_ctas, M, N, K):

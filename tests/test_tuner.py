@@ -52,8 +52,8 @@ def test_table_file_feeds_the_plan(tmp_path):
 def test_dense_candidates():
     c = tuner.dense_candidates(4096, 4096, 4096)
     assert (2, 0) in c and (256, 0) in c and (128, 0) in c
-    assert all(tr in (2, 128, 256) and 0 <= g < 148 and (tr != 2 or g % 2 == 0) for tr, g in c)
-    assert all(tr != 2 for tr, _ in tuner.dense_candidates(512, 512, 272))
+    assert all(tr in (2, 3, 128, 256) and 0 <= g < 148 and (tr not in (2, 3) or g % 2 == 0) for tr, g in c)
+    assert all(tr not in (2, 3) for tr, _ in tuner.dense_candidates(512, 512, 272))
 
 
 @pytest.mark.gpu
