@@ -38,6 +38,7 @@
 // (projects/skinny_gemm/skinny_gemm_caller.cu:343-405).
 #include <cuda_bf16.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -281,6 +282,27 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
             const int seg_end = tile_end < hi ? tile_end : hi;
             const bool from_k0 = kb0 == 0, to_k_end = seg_end == tile_end;
             const int buf = seg & 1;
+            // A tile whose head I hold (always my last segment) is mine to finish.  Its other parts were computed by
+            // the following CTAs at the START of their ranges, so their flags are normally up long before my last MMA:
+            // find them and poll them now, one lane per flag (each poll is an L2 round trip), while the MMAs run.
+            int last_partner = cta;
+            if (from_k0 && !to_k_end) {
+                while (last_partner + 1 < static_cast<int>(gridDim.x) && p.range_begin[last_partner + 1] < tile_end) last_partner++;
+                for (int base = cta + 1; base <= last_partner && live; base += 32) {
+                    const int j = base + lane;
+                    bool ok = true;
+                    if (j <= last_partner && p.range_begin[j] != p.range_begin[j + 1]) {     // an empty range holds nothing
+                        const unsigned* f = p.words + 8 + 2 * j + e;
+                        const uint64_t t0 = globaltimer_ns(), budget = wait_budget_ns();
+                        unsigned spins = 0;
+                        while (static_cast<int>(ld_acquire_gpu_u32(f) - (epoch + 1)) < 0) {
+                            if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > budget) { ok = false; break; }
+                        }
+                    }
+                    if (!__all_sync(0xffffffffu, ok)) live = false;
+                }
+                if (!live) { *abort_flag = 1; if (lane == 0) report_timeout(p.status); }
+            }
             bool ok = mbar_wait(acc_full0 + 8 * buf, (seg >> 1) & 1);
             if (!ok) { *abort_flag = 1; report_timeout(p.status); }
             if (*abort_flag != 0) { live = false; break; }
@@ -305,20 +327,21 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
                 }
             } else {
                 const float sc = __ldg(pr.scale_a) * __ldg(pr.scale_b);
-                // partners: the CTAs after this one whose ranges hold the rest of the tile's K range, in K order
-                int last_partner = cta;
-                if (!to_k_end)
-                    while (last_partner + 1 < static_cast<int>(gridDim.x) && p.range_begin[last_partner + 1] < tile_end) last_partner++;
-                for (int j = cta + 1; j <= last_partner && live; j++) {
-                    if (p.range_begin[j] == p.range_begin[j + 1]) continue;     // an empty range holds nothing
-                    const unsigned* f = p.words + 8 + 2 * j + e;
-                    const uint64_t t0 = globaltimer_ns(), budget = wait_budget_ns();
-                    unsigned spins = 0;
-                    while (static_cast<int>(ld_acquire_gpu_u32(f) - (epoch + 1)) < 0) {
-                        if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > budget) { live = false; break; }
+                // the partners' parts of 32 columns of my row, added in K order; the loads of a part are issued
+                // together (eight independent 16-byte loads per lane)
+                auto add_parts = [&](int c0, float* v) {
+                    if (lane < pr.M) {
+                        for (int j = cta + 1; j <= last_partner; j++) {
+                            if (p.range_begin[j] == p.range_begin[j + 1]) continue;
+                            const float4* src = reinterpret_cast<const float4*>(p.partial + static_cast<size_t>(j) * SLOT_FLOATS + lane * MAX_R + c0);
+                            float4 t[8];
+#pragma unroll
+                            for (int q = 0; q < 8; q++) t[q] = __ldcg(src + q);
+#pragma unroll
+                            for (int q = 0; q < 8; q++) { v[4 * q] += t[q].x; v[4 * q + 1] += t[q].y; v[4 * q + 2] += t[q].z; v[4 * q + 3] += t[q].w; }
+                        }
                     }
-                }
-                if (!live) { *abort_flag = 1; if (lane == 0) report_timeout(p.status); }
+                };
                 if (p.push.world > 0) {
                     // fused delivery: warp e takes whole 128-column blocks (R is a multiple of 128 here), keeps the
                     // block's bf16 values packed in registers and hands them to the encoder
@@ -329,17 +352,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
                         for (int c = 0; c < 4; c++) {
                             float v[32];
                             tmem_ld32(taddr + b0 + 32 * c, v);
-                            if (lane < pr.M && live) {
-                                for (int j = cta + 1; j <= last_partner; j++) {
-                                    if (p.range_begin[j] == p.range_begin[j + 1]) continue;
-                                    const float4* src = reinterpret_cast<const float4*>(p.partial + static_cast<size_t>(j) * SLOT_FLOATS + lane * MAX_R + b0 + 32 * c);
-#pragma unroll
-                                    for (int q = 0; q < 8; q++) {
-                                        const float4 t = __ldcg(src + q);
-                                        v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
-                                    }
-                                }
-                            }
+                            add_parts(b0 + 32 * c, v);
 #pragma unroll
                             for (int j = 0; j < 16; j++) {
                                 const __nv_bfloat162 h2 = __floats2bfloat162_rn(v[2 * j] * sc, v[2 * j + 1] * sc);
@@ -348,24 +361,14 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
                                 amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w << 16)), fabsf(__uint_as_float(w & 0xFFFF0000u))));
                             }
                         }
-                        if (lane < pr.M && live) push_block128(p.push, packed, amax, static_cast<size_t>(lane) * pr.N + n0 + b0);
+                        if (lane < pr.M) push_block128(p.push, packed, amax, static_cast<size_t>(lane) * pr.N + n0 + b0);
                     }
-                } else
-                for (int c0 = 32 * e; c0 < pr.R; c0 += 64) {
-                    float v[32];
-                    tmem_ld32(taddr + c0, v);
-                    if (lane < pr.M && live) {
-                        for (int j = cta + 1; j <= last_partner; j++) {
-                            if (p.range_begin[j] == p.range_begin[j + 1]) continue;
-                            const float4* src = reinterpret_cast<const float4*>(p.partial + static_cast<size_t>(j) * SLOT_FLOATS + lane * MAX_R + c0);
-#pragma unroll
-                            for (int q = 0; q < 8; q++) {
-                                const float4 t = __ldcg(src + q);
-                                v[4 * q] += t.x; v[4 * q + 1] += t.y; v[4 * q + 2] += t.z; v[4 * q + 3] += t.w;
-                            }
-                        }
-                        const int valid = pr.R - c0 < 32 ? pr.R - c0 : 32;
-                        store_chunk(pr, v, sc, lane, n0 + c0, valid);
+                } else {
+                    for (int c0 = 32 * e; c0 < pr.R; c0 += 64) {
+                        float v[32];
+                        tmem_ld32(taddr + c0, v);
+                        add_parts(c0, v);
+                        if (lane < pr.M) store_chunk(pr, v, sc, lane, n0 + c0, pr.R - c0 < 32 ? pr.R - c0 : 32);
                     }
                 }
             }
@@ -545,11 +548,15 @@ static int run(const rdb_skinny_problem* pr, int count, cudaStream_t stream, con
     cfg.blockDim = dim3(NUM_THREADS, 1, 1);
     cfg.dynamicSmemBytes = SMEM_BYTES;
     cfg.stream = stream;
+    // A CTA that owns a shared tile waits for parts that HIGHER-numbered CTAs compute at the very start of their
+    // ranges, so those CTAs must get onto the GPU: the cooperative launch makes the runtime guarantee it (and refuse
+    // a grid that cannot be resident).  RDB_GROUPED_PLAIN_LAUNCH=1 selects a plain launch, for measurements.
+    static const bool plain_launch = [] { const char* v = getenv("RDB_GROUPED_PLAIN_LAUNCH"); return v && v[0] == '1'; }();
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeCooperative;
     attr[0].val.cooperative = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = plain_launch ? 0 : 1;
     if (cudaLaunchKernelEx(&cfg, skinny_grouped_kernel, prm) != cudaSuccess) {
         cudaGetLastError();
         return RDB_CUDA_ERROR;
