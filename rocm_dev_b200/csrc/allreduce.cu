@@ -62,6 +62,15 @@ constexpr int kGroup = 512;               // elements per work item: 4 blocks of
 constexpr size_t kOneShotMaxElems = 1u << 20;
 constexpr int kThreads = 256;
 constexpr int kBlocksPerSm = 4;     // resident blocks per SM the grids are sized for
+// One-shot transport (small messages, latency-bound): a group of 512 elements travels as 5 lines of 128 bytes.
+// A line is written by ONE store instruction (eight lanes x 16 bytes) and read by one load instruction, so it
+// crosses NVLink and is observed as a unit; its last 8 bytes hold the call's epoch twice.  The receiver polls
+// the lines themselves: no separate flag, and no system-wide fence between the data and its "valid" mark - that
+// fence, not the bytes, was what a small allreduce took its time for (~10 us per hand-over).  Line l carries the
+// code chunks (16 bytes = 16 elements each) 7l .. 7l+6 of the group in its first 112 bytes; bytes 112..119 of
+// lines 0 and 1 carry the four block scales.
+constexpr int kLlLines = 5;
+constexpr int kLlGroupBytes = kLlLines * 128;
 
 struct Layout {
     size_t slot_groups;   // groups one source rank may push into one slot
@@ -69,6 +78,8 @@ struct Layout {
     size_t off_s;         // [2][W][slot_groups * 4] floats
     size_t off_gather;    // [max_elems] bf16; the FP8 all-gather uses it as [max_elems] codes + scales at gather_scale_off
     size_t gather_scale_off;   // relative to off_gather
+    size_t ll_groups;     // groups one source rank may push into the flag-in-line area (one-shot calls)
+    size_t off_ll;        // [2][W][ll_groups][5 lines of 128 B]: one-shot staging whose every line carries its own flag
     size_t off_flags;     // [2 phases][2 epoch parities][kMaxWorld] uint32 flag words (epoch << 1 | failed), then 4 block
                           // counters at word 64 and 4 "a block of this launch gave up" words at word 68
     size_t bytes;
@@ -86,7 +97,9 @@ static Layout make_layout(int world, size_t max_elems) {
     L.off_s = round_up(L.off_q + 2 * static_cast<size_t>(world) * L.slot_groups * kGroup, 256);
     L.off_gather = round_up(L.off_s + 2 * static_cast<size_t>(world) * L.slot_groups * 4 * sizeof(float), 256);
     L.gather_scale_off = groups * kGroup;
-    L.off_flags = round_up(L.off_gather + groups * kGroup * 2, 256);
+    L.ll_groups = one;
+    L.off_ll = round_up(L.off_gather + groups * kGroup * 2, 256);
+    L.off_flags = round_up(L.off_ll + 2 * static_cast<size_t>(world) * L.ll_groups * kLlGroupBytes, 256);
     L.bytes = L.off_flags + 1024;
     return L;
 }
@@ -263,11 +276,15 @@ __device__ __forceinline__ bool wait_flags(const KParams& p, int which) {
         const unsigned* mine = reinterpret_cast<const unsigned*>(p.ws[p.rank] + p.L.off_flags) + (which * 2 + (p.epoch & 1u)) * kMaxWorld;
         bool ok = true;
         if (lane < p.world) {
-            const uint64_t t0 = globaltimer_ns(), budget = wait_budget_ns();
-            unsigned spins = 0, v;
             // epochs only grow; a flag at or beyond this call's epoch means "arrived"
-            while (static_cast<int>(((v = ld_acquire_sys(mine + lane)) >> 1) - p.epoch) < 0) {
-                if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > budget) { ok = false; break; }
+            unsigned v = ld_acquire_sys(mine + lane);
+            if (static_cast<int>((v >> 1) - p.epoch) < 0) {
+                // not there yet: only now read the clock and the budget (a global load that must stay off the fast path)
+                const uint64_t t0 = globaltimer_ns(), budget = wait_budget_ns();
+                unsigned spins = 0;
+                while (static_cast<int>(((v = ld_acquire_sys(mine + lane)) >> 1) - p.epoch) < 0) {
+                    if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > budget) { ok = false; break; }
+                }
             }
             if (ok && (v >> 1) == p.epoch && (v & 1u)) ok = false;   // that rank gave up before delivering
         }
@@ -528,6 +545,158 @@ __device__ __forceinline__ void stamp(const KParams& p, int slot) {
     }
 }
 
+// ------------------------------------------------------- one-shot, flag in line
+__device__ __forceinline__ void st_line16(void* addr, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_line16(const void* addr) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(addr) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ uint8_t* ll_slot(const KParams& p, uint8_t* ws, int src_rank, size_t g) {
+    return ws + p.L.off_ll + ((static_cast<size_t>(p.epoch & 1u) * p.world + src_rank) * p.L.ll_groups + g) * kLlGroupBytes;
+}
+
+// Every warp encodes its groups and stores each as five self-validating lines into the slot (this rank, group) of
+// EVERY rank's workspace, its own included.
+__device__ __forceinline__ void ll_push_body(const KParams& p) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
+    const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
+    for (size_t g = warp; g < p.groups; g += nwarps) {
+        uint4 in[2];
+        load_group(p.x, p.n, g, lane, in);
+        uint2 q[2];
+        float s[2];
+#pragma unroll
+        for (int h = 0; h < 2; h++) q[h] = encode8(in[h], s[h]);
+        const float sc0 = __shfl_sync(0xffffffffu, s[0], 0), sc1 = __shfl_sync(0xffffffffu, s[0], 16);
+        const float sc2 = __shfl_sync(0xffffffffu, s[1], 0), sc3 = __shfl_sync(0xffffffffu, s[1], 16);
+        const uint4 q16 = regroup16(q, lane);            // lane l: code chunk l (bytes [16 l, 16 l + 16) of the group)
+        // store instruction i: lane t writes 16 bytes at position t % 8 of line 4 i + t / 8
+#pragma unroll
+        for (int i = 0; i < 2; i++) {
+            const int line = 4 * i + (lane >> 3), pos = lane & 7;
+            const int chunk = 7 * line + pos;             // the code chunk this lane forwards (positions 0..6)
+            const int src = chunk < 32 ? chunk : 0;
+            uint4 v;
+            v.x = __shfl_sync(0xffffffffu, q16.x, src);
+            v.y = __shfl_sync(0xffffffffu, q16.y, src);
+            v.z = __shfl_sync(0xffffffffu, q16.z, src);
+            v.w = __shfl_sync(0xffffffffu, q16.w, src);
+            if (pos == 7) {
+                v.x = line == 0 ? __float_as_uint(sc0) : line == 1 ? __float_as_uint(sc2) : 0u;
+                v.y = line == 0 ? __float_as_uint(sc1) : line == 1 ? __float_as_uint(sc3) : 0u;
+                v.z = p.epoch;
+                v.w = p.epoch;
+            } else if (chunk >= 32) {
+                v = make_uint4(0u, 0u, 0u, 0u);
+            }
+            if (line < kLlLines) {
+                for (int k = 0; k < p.world; k++) {
+                    int peer = p.rank + 1 + k;            // start after myself: the remote lines leave first
+                    if (peer >= p.world) peer -= p.world;
+                    st_line16(ll_slot(p, p.ws[peer], p.rank, g) + line * 128 + pos * 16, v);
+                }
+            }
+        }
+    }
+}
+
+// Every warp takes its groups, waits (bounded) for the five lines of each rank in rank order, decodes them in the
+// layout they arrive in - lane t holds chunk 7 (t / 8) + t % 8 of lines 0..3, lanes 0..3 also chunks 28..31 of
+// line 4 - and accumulates exactly as reduce_body does (product and sum rounded separately, rank order).
+// Returns false if a wait ran out.
+__device__ __forceinline__ bool ll_reduce_body(const KParams& p) {
+    const int lane = threadIdx.x & 31;
+    const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
+    const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
+    const int pos = lane & 7, line_a = lane >> 3;
+    const bool has_a = pos < 7, has_b = lane < 4;         // a: chunk 7 line_a + pos;  b: chunk 28 + lane (line 4)
+    const int chunk_a = 7 * line_a + pos, chunk_b = 28 + lane;
+    bool all_ok = true;
+    for (size_t g = warp; g < p.groups; g += nwarps) {
+        float acc_a[16], acc_b[16];
+#pragma unroll
+        for (int i = 0; i < 16; i++) acc_a[i] = acc_b[i] = 0.0f;
+        bool ok = true;
+        for (int r = 0; r < p.world && ok; r++) {
+            const uint8_t* slot = ll_slot(p, p.ws[p.rank], r, g);
+            uint4 va, vb = make_uint4(0u, 0u, 0u, 0u);
+            uint64_t t0 = 0, budget = 0;
+            unsigned spins = 0;
+            while (true) {
+                va = ld_line16(slot + line_a * 128 + pos * 16);
+                if (lane < 8) vb = ld_line16(slot + 4 * 128 + pos * 16);
+                bool valid = true;
+                if (pos == 7) valid = va.z == p.epoch && va.w == p.epoch && (lane >= 8 || (vb.z == p.epoch && vb.w == p.epoch));
+                if (__all_sync(0xffffffffu, valid)) break;
+                if (spins == 0) { t0 = globaltimer_ns(); budget = wait_budget_ns(); }
+                // `spins` is the same in every lane, so the whole warp takes this branch together and agrees on giving up
+                if ((++spins & 0x3F) == 0 && __any_sync(0xffffffffu, globaltimer_ns() - t0 > budget)) { ok = false; break; }
+            }
+            if (!ok) break;
+            // the four block scales sit in position 7 of lines 0 and 1 (lanes 7 and 15)
+            const float s0 = __uint_as_float(__shfl_sync(0xffffffffu, va.x, 7)), s1 = __uint_as_float(__shfl_sync(0xffffffffu, va.y, 7));
+            const float s2 = __uint_as_float(__shfl_sync(0xffffffffu, va.x, 15)), s3 = __uint_as_float(__shfl_sync(0xffffffffu, va.y, 15));
+            float v[8];
+            if (has_a) {
+                const int blk = chunk_a >> 3;               // 8 chunks of 16 elements per block of 128
+                const float sc = blk == 0 ? s0 : blk == 1 ? s1 : blk == 2 ? s2 : s3;
+                decode8(make_uint2(va.x, va.y), v);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc_a[i] = __fadd_rn(acc_a[i], __fmul_rn(v[i], sc));
+                decode8(make_uint2(va.z, va.w), v);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc_a[8 + i] = __fadd_rn(acc_a[8 + i], __fmul_rn(v[i], sc));
+            }
+            if (has_b) {
+                decode8(make_uint2(vb.x, vb.y), v);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc_b[i] = __fadd_rn(acc_b[i], __fmul_rn(v[i], s3));   // chunks 28..31: block 3
+                decode8(make_uint2(vb.z, vb.w), v);
+#pragma unroll
+                for (int i = 0; i < 8; i++) acc_b[8 + i] = __fadd_rn(acc_b[8 + i], __fmul_rn(v[i], s3));
+            }
+        }
+        if (!ok) {
+            if (lane == 0) report_timeout(p.status);
+            all_ok = false;
+            continue;
+        }
+        auto store16 = [&](int chunk, const float* a) {
+            const size_t e0 = g * kGroup + static_cast<size_t>(chunk) * 16;
+            if (e0 >= p.n) return;                          // n is a multiple of 128: a chunk is in or out as a whole
+            uint32_t o[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const __nv_bfloat162 b = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
+                o[i] = *reinterpret_cast<const uint32_t*>(&b);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(p.out + e0);
+            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
+            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
+        };
+        if (has_a) store16(chunk_a, acc_a);
+        if (has_b) store16(chunk_b, acc_b);
+    }
+    return all_ok;
+}
+
+// One-shot call in one launch: no warp depends on any other warp of this grid, so the launch is an ordinary one of
+// any size.  The two halves also exist as separate launches for drivers that emulate several ranks on one GPU.
+__global__ void __launch_bounds__(kThreads) ar_ll_oneshot_kernel(const KParams p) {
+    stamp(p, 0);
+    ll_push_body(p);
+    stamp(p, 1);
+    ll_reduce_body(p);
+    stamp(p, 3);
+}
+__global__ void __launch_bounds__(kThreads) ar_ll_push_kernel(const KParams p) { ll_push_body(p); }
+__global__ void __launch_bounds__(kThreads) ar_ll_reduce_kernel(const KParams p) { ll_reduce_body(p); }
+
 __global__ void __launch_bounds__(kThreads, kBlocksPerSm) ar_fused_kernel(const KParams p) {
     stamp(p, 0);
     push_body(p);
@@ -623,8 +792,10 @@ static int grid_for(size_t warps_needed, int sm_count, int blocks_per_sm = kBloc
     return static_cast<int>(blocks);
 }
 
+// `prepushed`: the one-shot call's encoded input was delivered by another kernel into the flag-guarded staging area
+// (GEMM epilogue), so its reduce step is the flag-waiting one; ordinary one-shot calls use the flag-in-line transport.
 static int run_phase(Ctx* c, int phase, const uint16_t* x, uint16_t* out, size_t n, int algo, unsigned epoch,
-                     cudaStream_t stream) {
+                     cudaStream_t stream, bool prepushed = false) {
     int err = 0;
     DeviceInfo* info = device_info(&err);
     if (!info) return err;
@@ -652,11 +823,27 @@ static int run_phase(Ctx* c, int phase, const uint16_t* x, uint16_t* out, size_t
         if (o >= lo && o + n * 2 <= lo + c->reg_bytes)
             for (int i = 0; i < c->world; i++) p.reg[i] = c->reg[i] + (o - lo);
     }
+    if (p.one_shot && !prepushed) {
+        // no block of these kernels waits for another block of the same grid: ordinary launches, any grid
+        const int grid = grid_for(p.groups, info->sm_count);
+        if (phase == 0) ar_ll_oneshot_kernel<<<grid, kThreads, 0, stream>>>(p);
+        else if (phase == 1) ar_ll_push_kernel<<<grid, kThreads, 0, stream>>>(p);
+        else if (phase == 2) ar_ll_reduce_kernel<<<grid, kThreads, 0, stream>>>(p);
+        return cudaGetLastError() == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
+    }
     if (phase == 0) {
         void* args[] = {&p};
         const int grid = grid_for(p.groups, info->sm_count, fused_blocks_per_sm());
-        if (cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ar_fused_kernel), dim3(grid), dim3(kThreads), args, 0, stream) !=
-            cudaSuccess) {
+        // RDB_AR_PLAIN_LAUNCH=1: an ordinary launch of the same grid (residency then rests on the occupancy cap alone)
+        static const bool plain_launch = [] { const char* v = getenv("RDB_AR_PLAIN_LAUNCH"); return v && v[0] == '1'; }();
+        cudaError_t e;
+        if (plain_launch) {
+            ar_fused_kernel<<<grid, kThreads, 0, stream>>>(p);
+            e = cudaGetLastError();
+        } else {
+            e = cudaLaunchCooperativeKernel(reinterpret_cast<void*>(ar_fused_kernel), dim3(grid), dim3(kThreads), args, 0, stream);
+        }
+        if (e != cudaSuccess) {
             cudaGetLastError();
             return RDB_CUDA_ERROR;
         }
@@ -722,7 +909,7 @@ int finish_prepushed(void* ctx, uint16_t* out, cudaStream_t stream) {
     const size_t n = c->pending_n;
     c->pending_n = 0;
     // phase 2 of a one-shot call: the reduce kernel waits for every rank's "pushed" flag and writes `out`
-    return run_phase(c, 2, nullptr, out, n, 1, c->pending_epoch, stream);
+    return run_phase(c, 2, nullptr, out, n, 1, c->pending_epoch, stream, true);
 }
 
 }  // namespace ar

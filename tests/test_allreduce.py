@@ -398,7 +398,33 @@ def test_a_wait_that_runs_out_is_reported_and_leaves_everything_usable(cuda_devi
                 assert not outs[1].any() and not outs[0].any()                          # nobody copied a partial result
             finally:
                 assert L.rdb_set_wait_budget_ns(1_000_000_000) == 0
+        # the same for the one-shot transport, whose receivers poll the data lines themselves: rank 0 reduces while
+        # rank 1's lines are missing -> its wait gives up, reports, and writes nothing for the groups it could not finish
+        with torch.cuda.device(cuda_device):
+            assert L.rdb_set_wait_budget_ns(2_000_000) == 0
+            try:
+                epoch = {int(L.rdb_ar_begin_call(c)) for c in lr.ctx}.pop()
+                outs[0].zero_()
+                args1 = lambda r: (xs[r].data_ptr(), outs[r].data_ptr(), n, 1, stream)   # noqa: E731
+                check(L.rdb_ar_phase(lr.ctx[0], 1, epoch, *args1(0)), "ll push 0")
+                check(L.rdb_ar_phase(lr.ctx[0], 2, epoch, *args1(0)), "ll reduce 0")
+                torch.cuda.synchronize()
+                assert L.rdb_device_status() == 10 and not outs[0].any()
+                check(L.rdb_ar_phase(lr.ctx[1], 1, epoch, *args1(1)), "ll push 1")      # the late rank still completes
+                check(L.rdb_ar_phase(lr.ctx[1], 2, epoch, *args1(1)), "ll reduce 1")
+                torch.cuda.synchronize()
+                assert L.rdb_device_status() == 0
+                want1, _, _ = oracle.allreduce_fp8(np.stack([_bits(x) for x in xs]))
+                assert np.array_equal(_bits(outs[1]), want1)
+            finally:
+                assert L.rdb_set_wait_budget_ns(1_000_000_000) == 0
         for rep in range(2):                                                            # GPU and contexts are reusable
+            got = lr.all_reduce(xs, algo=1)
+            torch.cuda.synchronize()
+            assert L.rdb_device_status() == 0
+            want, _, _ = oracle.allreduce_fp8(np.stack([_bits(x) for x in xs]))
+            assert np.array_equal(_bits(got[0]), want) and np.array_equal(_bits(got[1]), want)
+        for rep in range(2):
             got = lr.all_reduce(xs, algo=2)
             torch.cuda.synchronize()
             assert L.rdb_device_status() == 0
