@@ -343,9 +343,11 @@ int rdb_ar_set_trace(void *ctx, unsigned long long *device_buffer16);
  * rdb_device_status() after a call tells whether `out` is valid.
  *
  * Collective: every rank calls it with the same n (a multiple of 128, at most
- * max_elems) and algo (0 automatic: one-shot up to 2^19 elements - up to 2^20
- * with two ranks - when out is given, else two-shot; 1 one-shot: every rank
- * receives and reduces everything, n <= 2^20; 2 two-shot: FP8 reduce-scatter
+ * max_elems) and algo (0 automatic: one-shot up to 2^22 elements on up to four
+ * ranks, 2^21 on more, when out is given, else two-shot; 1 one-shot: every rank
+ * receives and reduces everything, n <= 2^22 - the encoded groups travel as
+ * 128-byte lines that carry their own valid mark, so the receivers poll the
+ * data itself and no fence or flag hand-over is paid; 2 two-shot: FP8 reduce-scatter
  * then bf16 all-gather; 3 two-shot with an FP8 all-gather: the reduced bf16
  * shard is block-quantised a second time before it travels, so the result is
  * decode(encode(result of algo 2)) - fewer bytes on the wire, one more
@@ -364,7 +366,7 @@ const uint16_t *rdb_ar_result(void *ctx);
  * every rank's staging slots - the allreduce's "read x, encode, push" step and
  * the round trip of P_r through HBM disappear; the second launch waits for all
  * ranks, decodes, sums in rank order and writes `out` (M*N bf16).  problem->D
- * is not written (may be NULL).  Requires N % 128 == 0 and M*N <= 2^20 (the
+ * is not written (may be NULL).  Requires N % 128 == 0 and M*N <= 2^22 (the
  * one-shot limit) and <= the context's max_elems.  The result equals
  * rdb_ar_allreduce (one-shot) applied to the D that
  * rdb_skinny_gemm_fp8_grouped(problem, 1) writes, bit for bit.  Collective:

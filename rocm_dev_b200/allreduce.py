@@ -209,10 +209,19 @@ class Fp8AllReduce:
         if out is None:
             out = torch.empty_like(x)
         assert out.dtype == torch.bfloat16 and out.is_contiguous() and out.numel() == n
-        with torch.cuda.device(self.device):
-            check(lib().rdb_ar_allreduce(self.ctx, x.data_ptr(), out.data_ptr(), n, algo,
-                                         torch.cuda.current_stream(self.device).cuda_stream), "rdb_ar_allreduce")
-            if check_status:
+        # a small call is a few microseconds of device time: keep the host path short (no device-context switch when
+        # this rank's device is already current)
+        if torch.cuda.current_device() == self.device.index:
+            code = lib().rdb_ar_allreduce(self.ctx, x.data_ptr(), out.data_ptr(), n, algo,
+                                          torch.cuda.current_stream().cuda_stream)
+        else:
+            with torch.cuda.device(self.device):
+                code = lib().rdb_ar_allreduce(self.ctx, x.data_ptr(), out.data_ptr(), n, algo,
+                                              torch.cuda.current_stream(self.device).cuda_stream)
+        if code != 0:
+            check(code, "rdb_ar_allreduce")
+        if check_status:
+            with torch.cuda.device(self.device):
                 check(lib().rdb_device_status(), "rdb_ar_allreduce (device status)")
         return out
 

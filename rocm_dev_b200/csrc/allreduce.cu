@@ -59,7 +59,7 @@ namespace ar {
 
 constexpr int kMaxWorld = 8;
 constexpr int kGroup = 512;               // elements per work item: 4 blocks of 128
-constexpr size_t kOneShotMaxElems = 1u << 20;
+constexpr size_t kOneShotMaxElems = 1u << 22;
 constexpr int kThreads = 256;
 constexpr int kBlocksPerSm = 4;     // resident blocks per SM the grids are sized for
 // One-shot transport (small messages, latency-bound): a group of 512 elements travels as 5 lines of 128 bytes.
@@ -865,10 +865,11 @@ static int check_call(Ctx* c, const uint16_t* x, uint16_t* out, size_t n, int& a
     if (n == 0 || n % 128 != 0) return RDB_BAD_SHAPE;
     if (n > c->max_elems) return RDB_SIZE_ABOVE_LIMIT;
     if (!aligned16(x) || (out && !aligned16(out))) return RDB_BAD_ALIGNMENT;
-    // one-shot up to 512 K elements (8 ranks, 1 MiB of bf16: 24.0 us against 26.6 us two-shot; at 2 MiB 32.2 against
-    // 29.6); with two ranks up to its size limit (2 MiB: 14.9 us against 24.3 us two-shot and 19.0 us NCCL)
-    if (algo == 0)
-        algo = (out != nullptr && (n <= kOneShotMaxElems / 2 || (c->world == 2 && n <= kOneShotMaxElems))) ? 1 : 2;
+    // one-shot (every rank receives everything, flag-in-line transport, ~5 us of device time for small messages)
+    // while the extra wire bytes - (W-1) x 1.25 n against (W-1)/W x 3 n for two-shot - cost less than the two
+    // fenced hand-overs of two-shot: measured ahead up to 4 Mi elements on 2 and 4 GPUs (8 MiB of bf16: 20.8 us
+    // against 43.6 us on 2 GPUs, 37.2 us against 50.6 us on 4); with more ranks the wire term doubles, so 2 Mi there
+    if (algo == 0) algo = (out != nullptr && n <= (c->world <= 4 ? kOneShotMaxElems : kOneShotMaxElems / 2)) ? 1 : 2;
     if (algo == 1 && n > kOneShotMaxElems) return RDB_SIZE_ABOVE_LIMIT;
     if ((algo == 1 || algo == 3) && out == nullptr) return RDB_INVALID_CONFIG;
     if (algo < 1 || algo > 3) return RDB_INVALID_CONFIG;

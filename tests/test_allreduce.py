@@ -146,6 +146,27 @@ def test_emulated_ranks_on_one_gpu(cuda_device, oracle, world, algo):
         lr.close()
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_automatic_choice_at_the_one_shot_limit(cuda_device, oracle, world):
+    """The largest message the automatic choice still sends one-shot (2^22 elements on up to four ranks, 2^21 on
+    more), one block less, and one block more (two-shot): all bit-exact."""
+    import rocm_dev_b200 as R
+    limit = (1 << 22) if world <= 4 else (1 << 21)
+    lr = R.LocalRanks(world, max_elems=limit + 128, device=cuda_device)
+    try:
+        for n in (limit - 128, limit, limit + 128):
+            xs = [torch.randn(n, generator=torch.Generator().manual_seed(3 * r + n % 1000)).bfloat16() for r in range(world)]
+            outs = lr.all_reduce([x.to(cuda_device) for x in xs], algo=0)
+            torch.cuda.synchronize()
+            assert R.lib().rdb_device_status() == 0
+            want, _, _ = oracle.allreduce_fp8(np.stack([_bits(x) for x in xs]))
+            for r in range(world):
+                assert np.array_equal(_bits(outs[r]), want), (world, n, r)
+    finally:
+        lr.close()
+
+
 def test_regather_variant_oracle_properties(oracle):
     """The FP8-all-gather variant is decode(encode(first variant)): idempotent
     (a second round trip changes nothing), exact on zero blocks, and within one
