@@ -716,7 +716,7 @@ __global__ void __launch_bounds__(kThreads, kBlocksPerSm) ar_fused_kernel(const 
 
 // Standalone encoder (the quantise step alone, for bit-exact tests and callers
 // that want the encoding): q [n] bytes, scales [n/128].
-__global__ void __launch_bounds__(kThreads) quantize_blocks128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
+__global__ void __launch_bounds__(kThreads, 6) quantize_blocks128_kernel(const __nv_bfloat16* __restrict__ x, uint8_t* __restrict__ q,
                                                                      float* __restrict__ scales, size_t n, size_t groups) {
     const int lane = threadIdx.x & 31;
     const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
@@ -1062,7 +1062,8 @@ int rdb_quantize_blocks128(const uint16_t* x, uint8_t* q, float* scales, size_t 
     rdb::DeviceInfo* info = rdb::device_info(&err);
     if (!info) return err;
     const size_t groups = (n + rdb::ar::kGroup - 1) / rdb::ar::kGroup;
-    rdb::ar::quantize_blocks128_kernel<<<rdb::ar::grid_for(groups, info->sm_count), rdb::ar::kThreads, 0,
+    // latency-bound: six resident blocks per SM (the register budget of the kernel) instead of the collectives' four
+    rdb::ar::quantize_blocks128_kernel<<<rdb::ar::grid_for(groups, info->sm_count, 6), rdb::ar::kThreads, 0,
                                          static_cast<cudaStream_t>(stream)>>>(
         reinterpret_cast<const __nv_bfloat16*>(x), q, scales, n, groups);
     return cudaGetLastError() == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;

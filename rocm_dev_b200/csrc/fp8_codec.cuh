@@ -40,7 +40,8 @@ struct BlockDivisor {
 #pragma unroll
             for (int i = 0; i < 8; i++) q[i] = div_fast(x[i]);
         } else {
-#pragma unroll 1
+            // also unrolled: a loop with a run-time index would put x and q into local memory - for the fast path too
+#pragma unroll
             for (int i = 0; i < 8; i++) q[i] = __fdiv_rn(x[i], s);
         }
     }
