@@ -81,7 +81,7 @@ struct Layout {
     size_t ll_groups;     // groups one source rank may push into the flag-in-line area (one-shot calls)
     size_t off_ll;        // [2][W][ll_groups][5 lines of 128 B]: one-shot staging whose every line carries its own flag
     size_t off_flags;     // [2 phases][2 epoch parities][kMaxWorld] uint32 flag words (epoch << 1 | failed), then 4 block
-                          // counters at word 64 and 4 "a block of this launch gave up" words at word 68
+                          // counters at word 64 (low 16 bits: blocks that finished, above: blocks that gave up)
     size_t bytes;
 };
 
@@ -239,17 +239,16 @@ __device__ __forceinline__ void publish_when_grid_done(const KParams& p, int whi
         const int lane = threadIdx.x;
         unsigned word = 0;
         if (lane == 0) {
-            unsigned* own = reinterpret_cast<unsigned*>(p.ws[p.rank] + p.L.off_flags);
-            unsigned* cnt = own + 64 + which * 2 + (p.epoch & 1u);   // two calls may be in flight
-            unsigned* bad = own + 68 + which * 2 + (p.epoch & 1u);
-            if (failed) atomicOr(bad, 1u);
+            // The block counter also carries the failure mark (bit 16 upwards), so the last block learns both from the
+            // one atomic it needs anyway.  No further fence before the flag stores: every block fenced its own stores
+            // before counting itself, the last block's atomic observes all those counts, and st.release orders the
+            // flag after everything that happened before it.
+            unsigned* cnt = reinterpret_cast<unsigned*>(p.ws[p.rank] + p.L.off_flags) + 64 + which * 2 + (p.epoch & 1u);   // two calls may be in flight
             __threadfence_system();
-            const unsigned old = atomicAdd(cnt, 1u);
-            if (old == gridDim.x - 1) {
-                const unsigned any_failed = atomicExch(bad, 0u);
+            const unsigned old = atomicAdd(cnt, failed ? 0x10001u : 1u);
+            if ((old & 0xFFFFu) == gridDim.x - 1) {
                 *cnt = 0;                      // ready for the next launch
-                __threadfence_system();
-                word = 0x80000000u | (any_failed & 1u);
+                word = 0x80000000u | (((old >> 16) != 0 || failed) ? 1u : 0u);
             }
         }
         word = __shfl_sync(0xffffffffu, word, 0);

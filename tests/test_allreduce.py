@@ -62,6 +62,38 @@ def test_two_rank_protocol_on_cpu(oracle, n):
     assert np.array_equal(res[0], want) and np.array_equal(res[1], want)
 
 
+def _gloo_rank_that_may_leave(rank, world, port, q):
+    """Rank 1 leaves before the handle exchange; rank 0 must get an error from the process group instead of waiting
+    for ever (the host-side form of a failed peer: nothing on a GPU is involved)."""
+    import datetime
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    if rank == 1:
+        q.put((1, "left"))
+        q.close()
+        q.join_thread()                          # the message is out; now disappear without a clean shutdown
+        os._exit(0)
+    try:
+        handles = [None] * world
+        dist.all_gather_object(handles, b"x" * 64)          # the exchange Fp8AllReduce's set-up performs
+        q.put((0, "no error"))
+    except Exception as e:  # noqa: BLE001
+        q.put((0, "error: " + type(e).__name__))
+
+
+def test_a_rank_that_leaves_before_set_up_is_an_error_not_a_hang():
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29700 + os.getpid() % 200
+    procs = [ctx.Process(target=_gloo_rank_that_may_leave, args=(r, 2, port, q)) for r in range(2)]
+    [p.start() for p in procs]
+    res = dict(q.get(timeout=60) for _ in range(2))
+    [p.join(timeout=30) for p in procs]
+    assert res[1] == "left" and res[0].startswith("error"), res
+
+
 def test_shard_groups_cover_every_group_once():
     from rocm_dev_b200.allreduce import shard_groups
     for n in (128, 512, 640, 8192, 8192 * 4096, 128 * 999):
