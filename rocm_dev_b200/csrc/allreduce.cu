@@ -62,13 +62,14 @@ constexpr int kGroup = 512;               // elements per work item: 4 blocks of
 constexpr size_t kOneShotMaxElems = 1u << 22;
 constexpr int kThreads = 256;
 constexpr int kBlocksPerSm = 4;     // resident blocks per SM the grids are sized for
-// One-shot transport (small messages, latency-bound): a group of 512 elements travels as 5 lines of 128 bytes.
-// A line is written by ONE store instruction (eight lanes x 16 bytes) and read by one load instruction, so it
-// crosses NVLink and is observed as a unit; its last 8 bytes hold the call's epoch twice.  The receiver polls
-// the lines themselves: no separate flag, and no system-wide fence between the data and its "valid" mark - that
-// fence, not the bytes, was what a small allreduce took its time for (~10 us per hand-over).  Line l carries the
-// code chunks (16 bytes = 16 elements each) 7l .. 7l+6 of the group in its first 112 bytes; bytes 112..119 of
-// lines 0 and 1 carry the four block scales.
+// Flag-in-line transport of the encoded groups: a group of 512 elements travels as 5 lines of 128 bytes.  A line
+// is written by ONE store instruction (eight lanes x 16 bytes) and read by one load instruction, so it crosses
+// NVLink and is observed as a unit; its last 8 bytes hold the call's epoch twice.  The receiver polls the lines
+// themselves: no separate flag, no grid-wide hand-over and no system-wide fence between the data and its "valid"
+// mark - that fence, not the bytes, was what a small allreduce took its time for (~10 us per hand-over).
+// Lane t of the encoder owns 16 code bytes of the group (8 of each 256-element half).  Lines 0..3: position
+// t % 8 < 7 of line t / 8 holds lane t's 16 bytes; position 7 holds {two block scales (lines 0 and 1), epoch,
+// epoch}.  Line 4: positions 0..3 hold the bytes of lanes 7, 15, 23, 31, position 7 the epoch pair.
 constexpr int kLlLines = 5;
 constexpr int kLlGroupBytes = kLlLines * 128;
 
@@ -78,8 +79,7 @@ struct Layout {
     size_t off_s;         // [2][W][slot_groups * 4] floats
     size_t off_gather;    // [max_elems] bf16; the FP8 all-gather uses it as [max_elems] codes + scales at gather_scale_off
     size_t gather_scale_off;   // relative to off_gather
-    size_t ll_groups;     // groups one source rank may push into the flag-in-line area (one-shot calls)
-    size_t off_ll;        // [2][W][ll_groups][5 lines of 128 B]: one-shot staging whose every line carries its own flag
+    size_t off_ll;        // [2][W][slot_groups][5 lines of 128 B]: staging whose every line carries its own valid mark
     size_t off_flags;     // [2 phases][2 epoch parities][kMaxWorld] uint32 flag words (epoch << 1 | failed), then 4 block
                           // counters at word 64 (low 16 bits: blocks that finished, above: blocks that gave up)
     size_t bytes;
@@ -97,9 +97,8 @@ static Layout make_layout(int world, size_t max_elems) {
     L.off_s = round_up(L.off_q + 2 * static_cast<size_t>(world) * L.slot_groups * kGroup, 256);
     L.off_gather = round_up(L.off_s + 2 * static_cast<size_t>(world) * L.slot_groups * 4 * sizeof(float), 256);
     L.gather_scale_off = groups * kGroup;
-    L.ll_groups = one;
     L.off_ll = round_up(L.off_gather + groups * kGroup * 2, 256);
-    L.off_flags = round_up(L.off_ll + 2 * static_cast<size_t>(world) * L.ll_groups * kLlGroupBytes, 256);
+    L.off_flags = round_up(L.off_ll + 2 * static_cast<size_t>(world) * L.slot_groups * kLlGroupBytes, 256);
     L.bytes = L.off_flags + 1024;
     return L;
 }
@@ -129,6 +128,7 @@ struct KParams {
     unsigned epoch;
     int one_shot;
     int fp8_gather;      // two-shot only: the all-gather carries re-encoded FP8 blocks instead of bf16
+    int lines;           // the encoded groups travel as self-validating 128-byte lines (no flag hand-over before the reduction)
     int push_order;
     const __nv_bfloat16* x;
     __nv_bfloat16* out;  // may be nullptr (two-shot: result stays in the gather area)
@@ -297,6 +297,73 @@ __device__ __forceinline__ bool wait_flags(const KParams& p, int which) {
     return ok_s != 0;
 }
 
+// ------------------------------------------------ flag-in-line transport
+__device__ __forceinline__ void st_line16(void* addr, uint4 v) {
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ uint4 ld_line16(const void* addr) {
+    uint4 v;
+    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(addr) : "memory");
+    return v;
+}
+// Slot of (source rank, position) in the line area of a workspace, for this call's parity.
+__device__ __forceinline__ uint8_t* line_slot(const KParams& p, uint8_t* ws, int src_rank, size_t slot_g) {
+    return ws + p.L.off_ll + ((static_cast<size_t>(p.epoch & 1u) * p.world + src_rank) * p.L.slot_groups + slot_g) * kLlGroupBytes;
+}
+
+// What the two store instructions of a group carry, per lane: `a` goes to line lane / 8, position lane % 8; `b`
+// (lanes 0..7 only) to line 4, position lane.  q: this lane's 8 + 8 code bytes, sc0..sc3: the group's block scales.
+__device__ __forceinline__ void lines_of_group(const uint2* q, float sc0, float sc1, float sc2, float sc3, unsigned epoch, int lane,
+                                               uint4& a, uint4& b) {
+    const int line = lane >> 3, pos = lane & 7;
+    a = make_uint4(q[0].x, q[0].y, q[1].x, q[1].y);
+    // the bytes of lanes 7, 15, 23, 31 (whose position in lines 0..3 is taken by the flag) ride in line 4
+    const int src = 8 * (lane & 3) + 7;
+    b.x = __shfl_sync(0xffffffffu, a.x, src);
+    b.y = __shfl_sync(0xffffffffu, a.y, src);
+    b.z = __shfl_sync(0xffffffffu, a.z, src);
+    b.w = __shfl_sync(0xffffffffu, a.w, src);
+    if (pos == 7) {
+        a.x = line == 0 ? __float_as_uint(sc0) : line == 1 ? __float_as_uint(sc2) : 0u;
+        a.y = line == 0 ? __float_as_uint(sc1) : line == 1 ? __float_as_uint(sc3) : 0u;
+        a.z = epoch;
+        a.w = epoch;
+    }
+    if (lane >= 4) b = lane == 7 ? make_uint4(0u, 0u, epoch, epoch) : make_uint4(0u, 0u, 0u, 0u);
+}
+
+// Waits (bounded) for the five lines of one group and returns this lane's code bytes (q0: first half of the group,
+// q1: second half) and the scales of its two blocks.  False when the budget ran out (decided for the whole warp).
+__device__ __forceinline__ bool fetch_lines(const uint8_t* slot, unsigned epoch, int lane, uint2& q0, uint2& q1, float& s0, float& s1) {
+    const int line = lane >> 3, pos = lane & 7;
+    uint4 va, vb = make_uint4(0u, 0u, 0u, 0u);
+    uint64_t t0 = 0, budget = 0;
+    unsigned spins = 0;
+    while (true) {
+        va = ld_line16(slot + line * 128 + pos * 16);
+        if (lane < 8) vb = ld_line16(slot + 4 * 128 + pos * 16);
+        bool valid = true;
+        if (pos == 7) valid = va.z == epoch && va.w == epoch && (lane != 7 || (vb.z == epoch && vb.w == epoch));
+        if (__all_sync(0xffffffffu, valid)) break;
+        if (spins == 0) { t0 = globaltimer_ns(); budget = wait_budget_ns(); }
+        // `spins` is the same in every lane, so the whole warp takes this branch together and agrees on giving up
+        if ((++spins & 0x3F) == 0 && __any_sync(0xffffffffu, globaltimer_ns() - t0 > budget)) return false;
+    }
+    // scales: position 7 of line 0 (lane 7) holds blocks 0, 1; of line 1 (lane 15) blocks 2, 3
+    const float sc0 = __uint_as_float(__shfl_sync(0xffffffffu, va.x, 7)), sc1 = __uint_as_float(__shfl_sync(0xffffffffu, va.y, 7));
+    const float sc2 = __uint_as_float(__shfl_sync(0xffffffffu, va.x, 15)), sc3 = __uint_as_float(__shfl_sync(0xffffffffu, va.y, 15));
+    // lanes 7, 15, 23, 31 take their bytes from line 4 (held by lanes 0..3)
+    const int src = lane >> 3;
+    const uint32_t bx = __shfl_sync(0xffffffffu, vb.x, src), by = __shfl_sync(0xffffffffu, vb.y, src);
+    const uint32_t bz = __shfl_sync(0xffffffffu, vb.z, src), bw = __shfl_sync(0xffffffffu, vb.w, src);
+    if (pos == 7) va = make_uint4(bx, by, bz, bw);
+    q0 = make_uint2(va.x, va.y);
+    q1 = make_uint2(va.z, va.w);
+    s0 = lane < 16 ? sc0 : sc1;
+    s1 = lane < 16 ? sc2 : sc3;
+    return true;
+}
+
 // ------------------------------------------------------------------ phase 1
 // Loads the two 16-byte pieces this lane owns of group g (zeros past the end).
 __device__ __forceinline__ void load_group(const __nv_bfloat16* x, size_t n, size_t g, int lane, uint4* in) {
@@ -374,6 +441,26 @@ __device__ __forceinline__ void push_body(const KParams& p) {
             // the four block scales of the group: (half 0: lanes 0, 16), (half 1: lanes 0, 16)
             const float s1 = __shfl_sync(0xffffffffu, s[0], 16), s3 = __shfl_sync(0xffffffffu, s[1], 16);
             const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + p.rank) * p.L.slot_groups + cur.slot_g;
+            if (p.lines) {
+                const float s0b = __shfl_sync(0xffffffffu, s[0], 0), s2b = __shfl_sync(0xffffffffu, s[1], 0);
+                uint4 la, lb;
+                lines_of_group(q, s0b, s1, s2b, s3, p.epoch, lane, la, lb);
+                for (int k = cur.first; k <= cur.last; k++) {
+                    int peer = k;
+                    if (p.one_shot) {                      // start after myself: the remote lines leave first
+                        peer = p.rank + 1 + k;
+                        if (peer >= p.world) peer -= p.world;
+                    }
+                    uint8_t* dst = line_slot(p, p.ws[peer], p.rank, cur.slot_g);
+                    st_line16(dst + (lane >> 3) * 128 + (lane & 7) * 16, la);
+                    if (lane < 8) st_line16(dst + 4 * 128 + lane * 16, lb);
+                }
+                have = have_next;
+                cur = nxt;
+                in[0] = in_next[0];
+                in[1] = in_next[1];
+                continue;
+            }
             const uint4 q16 = regroup16(q, lane);
             for (int peer = cur.first; peer <= cur.last; peer++) {
                 uint8_t* base = p.ws[peer];
@@ -393,17 +480,20 @@ __device__ __forceinline__ void push_body(const KParams& p) {
 
 __global__ void __launch_bounds__(kThreads) ar_push_kernel(const KParams p) {
     push_body(p);
-    publish_when_grid_done(p, 0, false);
+    if (!p.lines) publish_when_grid_done(p, 0, false);
 }
 
 // ------------------------------------------------------------------ phase 2
-__device__ __forceinline__ void reduce_body(const KParams& p, bool arrived) {
+// Returns false if a group's lines did not arrive within the budget (line transport only; with the flag-guarded
+// staging the caller has already waited and passes `arrived`).
+__device__ __forceinline__ bool reduce_body(const KParams& p, bool arrived) {
     const int lane = threadIdx.x & 31;
     const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
     const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
     const size_t gb = p.one_shot ? 0 : group_begin(p.rank, p.groups, p.world);
     const size_t ge = p.one_shot ? p.groups : group_begin(p.rank + 1, p.groups, p.world);
-    const uint8_t* mine = p.ws[p.rank];
+    uint8_t* mine = p.ws[p.rank];
+    bool all_ok = true;
     for (size_t g = gb + warp; arrived && g < ge; g += nwarps) {
         const size_t slot_g = g - gb;
         float acc[2][8];
@@ -411,12 +501,21 @@ __device__ __forceinline__ void reduce_body(const KParams& p, bool arrived) {
         for (int h = 0; h < 2; h++)
 #pragma unroll
             for (int i = 0; i < 8; i++) acc[h][i] = 0.0f;
+        bool ok = true;
         for (int r = 0; r < p.world; r++) {
-            const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + r) * p.L.slot_groups + slot_g;
-            const uint2* src = reinterpret_cast<const uint2*>(mine + p.L.off_q + slot * kGroup) + lane;
-            const uint2 q0 = __ldcg(src), q1 = __ldcg(src + 32);
-            const float* sc = reinterpret_cast<const float*>(mine + p.L.off_s) + slot * 4 + (lane >> 4);
-            const float s0 = __ldcg(sc), s1 = __ldcg(sc + 2);
+            uint2 q0, q1;
+            float s0, s1;
+            if (p.lines) {
+                if (!fetch_lines(line_slot(p, mine, r, slot_g), p.epoch, lane, q0, q1, s0, s1)) { ok = false; break; }
+            } else {
+                const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + r) * p.L.slot_groups + slot_g;
+                const uint2* src = reinterpret_cast<const uint2*>(mine + p.L.off_q + slot * kGroup) + lane;
+                q0 = __ldcg(src);
+                q1 = __ldcg(src + 32);
+                const float* sc = reinterpret_cast<const float*>(mine + p.L.off_s) + slot * 4 + (lane >> 4);
+                s0 = __ldcg(sc);
+                s1 = __ldcg(sc + 2);
+            }
             float v[8];
             decode8(q0, v);
 #pragma unroll
@@ -424,6 +523,11 @@ __device__ __forceinline__ void reduce_body(const KParams& p, bool arrived) {
             decode8(q1, v);
 #pragma unroll
             for (int i = 0; i < 8; i++) acc[1][i] = __fadd_rn(acc[1][i], __fmul_rn(v[i], s1));
+        }
+        if (!ok) {                     // a rank's lines are missing: report, deliver nothing for this group
+            if (lane == 0) report_timeout(p.status);
+            all_ok = false;
+            continue;
         }
         uint4 val[2];
 #pragma unroll
@@ -480,14 +584,15 @@ __device__ __forceinline__ void reduce_body(const KParams& p, bool arrived) {
             }
         }
     }
+    return all_ok;
 }
 
 __global__ void __launch_bounds__(kThreads) ar_reduce_kernel(const KParams p) {
-    const bool arrived = wait_flags(p, 0);
-    reduce_body(p, arrived);
+    const bool arrived = p.lines ? true : wait_flags(p, 0);       // lines are waited for group by group
+    const bool reduced = reduce_body(p, arrived);
     // also after a timeout, so that peers are not left waiting - with the failure bit set, so that
     // they do not take the missing shard for delivered
-    if (!p.one_shot) publish_when_grid_done(p, 1, !arrived);
+    if (!p.one_shot) publish_when_grid_done(p, 1, !arrived || !reduced);
 }
 
 // ------------------------------------------------------------------ phase 3
@@ -544,173 +649,34 @@ __device__ __forceinline__ void stamp(const KParams& p, int slot) {
     }
 }
 
-// ------------------------------------------------------- one-shot, flag in line
-__device__ __forceinline__ void st_line16(void* addr, uint4 v) {
-    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
-}
-__device__ __forceinline__ uint4 ld_line16(const void* addr) {
-    uint4 v;
-    asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(addr) : "memory");
-    return v;
-}
-
-__device__ __forceinline__ uint8_t* ll_slot(const KParams& p, uint8_t* ws, int src_rank, size_t g) {
-    return ws + p.L.off_ll + ((static_cast<size_t>(p.epoch & 1u) * p.world + src_rank) * p.L.ll_groups + g) * kLlGroupBytes;
-}
-
-// Every warp encodes its groups and stores each as five self-validating lines into the slot (this rank, group) of
-// EVERY rank's workspace, its own included.
-__device__ __forceinline__ void ll_push_body(const KParams& p) {
-    const int lane = threadIdx.x & 31;
-    const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
-    const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
-    for (size_t g = warp; g < p.groups; g += nwarps) {
-        uint4 in[2];
-        load_group(p.x, p.n, g, lane, in);
-        uint2 q[2];
-        float s[2];
-#pragma unroll
-        for (int h = 0; h < 2; h++) q[h] = encode8(in[h], s[h]);
-        const float sc0 = __shfl_sync(0xffffffffu, s[0], 0), sc1 = __shfl_sync(0xffffffffu, s[0], 16);
-        const float sc2 = __shfl_sync(0xffffffffu, s[1], 0), sc3 = __shfl_sync(0xffffffffu, s[1], 16);
-        const uint4 q16 = regroup16(q, lane);            // lane l: code chunk l (bytes [16 l, 16 l + 16) of the group)
-        // store instruction i: lane t writes 16 bytes at position t % 8 of line 4 i + t / 8
-#pragma unroll
-        for (int i = 0; i < 2; i++) {
-            const int line = 4 * i + (lane >> 3), pos = lane & 7;
-            const int chunk = 7 * line + pos;             // the code chunk this lane forwards (positions 0..6)
-            const int src = chunk < 32 ? chunk : 0;
-            uint4 v;
-            v.x = __shfl_sync(0xffffffffu, q16.x, src);
-            v.y = __shfl_sync(0xffffffffu, q16.y, src);
-            v.z = __shfl_sync(0xffffffffu, q16.z, src);
-            v.w = __shfl_sync(0xffffffffu, q16.w, src);
-            if (pos == 7) {
-                v.x = line == 0 ? __float_as_uint(sc0) : line == 1 ? __float_as_uint(sc2) : 0u;
-                v.y = line == 0 ? __float_as_uint(sc1) : line == 1 ? __float_as_uint(sc3) : 0u;
-                v.z = p.epoch;
-                v.w = p.epoch;
-            } else if (chunk >= 32) {
-                v = make_uint4(0u, 0u, 0u, 0u);
-            }
-            if (line < kLlLines) {
-                for (int k = 0; k < p.world; k++) {
-                    int peer = p.rank + 1 + k;            // start after myself: the remote lines leave first
-                    if (peer >= p.world) peer -= p.world;
-                    st_line16(ll_slot(p, p.ws[peer], p.rank, g) + line * 128 + pos * 16, v);
-                }
-            }
-        }
-    }
-}
-
-// Every warp takes its groups, waits (bounded) for the five lines of each rank in rank order, decodes them in the
-// layout they arrive in - lane t holds chunk 7 (t / 8) + t % 8 of lines 0..3, lanes 0..3 also chunks 28..31 of
-// line 4 - and accumulates exactly as reduce_body does (product and sum rounded separately, rank order).
-// Returns false if a wait ran out.
-__device__ __forceinline__ bool ll_reduce_body(const KParams& p) {
-    const int lane = threadIdx.x & 31;
-    const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
-    const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
-    const int pos = lane & 7, line_a = lane >> 3;
-    const bool has_a = pos < 7, has_b = lane < 4;         // a: chunk 7 line_a + pos;  b: chunk 28 + lane (line 4)
-    const int chunk_a = 7 * line_a + pos, chunk_b = 28 + lane;
-    bool all_ok = true;
-    for (size_t g = warp; g < p.groups; g += nwarps) {
-        float acc_a[16], acc_b[16];
-#pragma unroll
-        for (int i = 0; i < 16; i++) acc_a[i] = acc_b[i] = 0.0f;
-        bool ok = true;
-        for (int r = 0; r < p.world && ok; r++) {
-            const uint8_t* slot = ll_slot(p, p.ws[p.rank], r, g);
-            uint4 va, vb = make_uint4(0u, 0u, 0u, 0u);
-            uint64_t t0 = 0, budget = 0;
-            unsigned spins = 0;
-            while (true) {
-                va = ld_line16(slot + line_a * 128 + pos * 16);
-                if (lane < 8) vb = ld_line16(slot + 4 * 128 + pos * 16);
-                bool valid = true;
-                if (pos == 7) valid = va.z == p.epoch && va.w == p.epoch && (lane >= 8 || (vb.z == p.epoch && vb.w == p.epoch));
-                if (__all_sync(0xffffffffu, valid)) break;
-                if (spins == 0) { t0 = globaltimer_ns(); budget = wait_budget_ns(); }
-                // `spins` is the same in every lane, so the whole warp takes this branch together and agrees on giving up
-                if ((++spins & 0x3F) == 0 && __any_sync(0xffffffffu, globaltimer_ns() - t0 > budget)) { ok = false; break; }
-            }
-            if (!ok) break;
-            // the four block scales sit in position 7 of lines 0 and 1 (lanes 7 and 15)
-            const float s0 = __uint_as_float(__shfl_sync(0xffffffffu, va.x, 7)), s1 = __uint_as_float(__shfl_sync(0xffffffffu, va.y, 7));
-            const float s2 = __uint_as_float(__shfl_sync(0xffffffffu, va.x, 15)), s3 = __uint_as_float(__shfl_sync(0xffffffffu, va.y, 15));
-            float v[8];
-            if (has_a) {
-                const int blk = chunk_a >> 3;               // 8 chunks of 16 elements per block of 128
-                const float sc = blk == 0 ? s0 : blk == 1 ? s1 : blk == 2 ? s2 : s3;
-                decode8(make_uint2(va.x, va.y), v);
-#pragma unroll
-                for (int i = 0; i < 8; i++) acc_a[i] = __fadd_rn(acc_a[i], __fmul_rn(v[i], sc));
-                decode8(make_uint2(va.z, va.w), v);
-#pragma unroll
-                for (int i = 0; i < 8; i++) acc_a[8 + i] = __fadd_rn(acc_a[8 + i], __fmul_rn(v[i], sc));
-            }
-            if (has_b) {
-                decode8(make_uint2(vb.x, vb.y), v);
-#pragma unroll
-                for (int i = 0; i < 8; i++) acc_b[i] = __fadd_rn(acc_b[i], __fmul_rn(v[i], s3));   // chunks 28..31: block 3
-                decode8(make_uint2(vb.z, vb.w), v);
-#pragma unroll
-                for (int i = 0; i < 8; i++) acc_b[8 + i] = __fadd_rn(acc_b[8 + i], __fmul_rn(v[i], s3));
-            }
-        }
-        if (!ok) {
-            if (lane == 0) report_timeout(p.status);
-            all_ok = false;
-            continue;
-        }
-        auto store16 = [&](int chunk, const float* a) {
-            const size_t e0 = g * kGroup + static_cast<size_t>(chunk) * 16;
-            if (e0 >= p.n) return;                          // n is a multiple of 128: a chunk is in or out as a whole
-            uint32_t o[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const __nv_bfloat162 b = __floats2bfloat162_rn(a[2 * i], a[2 * i + 1]);
-                o[i] = *reinterpret_cast<const uint32_t*>(&b);
-            }
-            uint4* dst = reinterpret_cast<uint4*>(p.out + e0);
-            dst[0] = make_uint4(o[0], o[1], o[2], o[3]);
-            dst[1] = make_uint4(o[4], o[5], o[6], o[7]);
-        };
-        if (has_a) store16(chunk_a, acc_a);
-        if (has_b) store16(chunk_b, acc_b);
-    }
-    return all_ok;
-}
-
-// One-shot call in one launch: no warp depends on any other warp of this grid, so the launch is an ordinary one of
-// any size.  The two halves also exist as separate launches for drivers that emulate several ranks on one GPU.
-__global__ void __launch_bounds__(kThreads) ar_ll_oneshot_kernel(const KParams p) {
-    stamp(p, 0);
-    ll_push_body(p);
-    stamp(p, 1);
-    ll_reduce_body(p);
-    stamp(p, 3);
-}
-__global__ void __launch_bounds__(kThreads) ar_ll_push_kernel(const KParams p) { ll_push_body(p); }
-__global__ void __launch_bounds__(kThreads) ar_ll_reduce_kernel(const KParams p) { ll_reduce_body(p); }
-
 __global__ void __launch_bounds__(kThreads, kBlocksPerSm) ar_fused_kernel(const KParams p) {
     stamp(p, 0);
     push_body(p);
     stamp(p, 1);
-    publish_when_grid_done(p, 0, false);
-    const bool arrived = wait_flags(p, 0);
+    bool arrived = true;
+    if (!p.lines) {                    // flag-guarded staging: one hand-over before the reduction
+        publish_when_grid_done(p, 0, false);
+        arrived = wait_flags(p, 0);
+    }
     stamp(p, 2);
-    reduce_body(p, arrived);
+    const bool reduced = reduce_body(p, arrived);
     stamp(p, 3);
     if (p.one_shot) return;
-    publish_when_grid_done(p, 1, !arrived);
+    publish_when_grid_done(p, 1, !arrived || !reduced);
     const bool gathered = wait_flags(p, 1);
     stamp(p, 4);
     if (gathered) copy_out_body(p);
     stamp(p, 5);
+}
+
+// One-shot call over the line transport: a warp pushes its groups, then reduces the same groups as the lines of all
+// ranks arrive.  No block waits for another block of this grid, so the launch is an ordinary one of any size.
+__global__ void __launch_bounds__(kThreads) ar_oneshot_lines_kernel(const KParams p) {
+    stamp(p, 0);
+    push_body(p);
+    stamp(p, 1);
+    reduce_body(p, true);
+    stamp(p, 3);
 }
 
 // Standalone encoder (the quantise step alone, for bit-exact tests and callers
@@ -822,12 +788,12 @@ static int run_phase(Ctx* c, int phase, const uint16_t* x, uint16_t* out, size_t
         if (o >= lo && o + n * 2 <= lo + c->reg_bytes)
             for (int i = 0; i < c->world; i++) p.reg[i] = c->reg[i] + (o - lo);
     }
-    if (p.one_shot && !prepushed) {
-        // no block of these kernels waits for another block of the same grid: ordinary launches, any grid
-        const int grid = grid_for(p.groups, info->sm_count);
-        if (phase == 0) ar_ll_oneshot_kernel<<<grid, kThreads, 0, stream>>>(p);
-        else if (phase == 1) ar_ll_push_kernel<<<grid, kThreads, 0, stream>>>(p);
-        else if (phase == 2) ar_ll_reduce_kernel<<<grid, kThreads, 0, stream>>>(p);
+    // Transport of the FP8 leg: self-validating lines for one-shot calls; for two-shot calls when RDB_AR_LINES=1
+    // (5 lines carry 528 bytes: 21 % more wire bytes against one hand-over less); never for pre-pushed calls.
+    static const bool two_shot_lines = [] { const char* v = getenv("RDB_AR_LINES"); return v && v[0] == '1'; }();
+    p.lines = (!prepushed && (p.one_shot || two_shot_lines)) ? 1 : 0;
+    if (p.one_shot && p.lines && phase == 0) {
+        ar_oneshot_lines_kernel<<<grid_for(p.groups, info->sm_count), kThreads, 0, stream>>>(p);
         return cudaGetLastError() == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
     }
     if (phase == 0) {
