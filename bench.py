@@ -227,7 +227,7 @@ def run_gpu(args):
     # A grouped launch streams all of its problems at once, so each of them needs weights of its own for the
     # stream to stay L2-cold: one set of the four matrices per M, and two such groups alternating between steps.
     weights, acts, outs = make_inputs(torch, quant, dev, sets=2 if args.single else 2 * len(MS))
-    flags = R.OVERLAP_PRIOR_KERNEL   # weights are never written inside the timed region
+    flags = 0 if args.no_overlap else R.OVERLAP_PRIOR_KERNEL   # weights are never written inside the timed region
 
     def problems_of(M, wset):
         return [(acts[(M, K)][0], wset[si][0], acts[(M, K)][1], wset[si][1], outs[(M, N)])
@@ -261,13 +261,13 @@ def run_gpu(args):
         sets = weights[parity * half:(parity + 1) * half]
         if mode == "grouped":
             probs = [pr for mi, M in enumerate(MS) for pr in problems_of(M, sets[mi])]
-            code = R.skinny_gemm_fp8_grouped(probs)
+            code = R.skinny_gemm_fp8_grouped(probs, flags)
             if code != 0:
                 raise RuntimeError(f"grouped skinny GEMM returned {code}")
             return 1
         if mode == "layer":
             for mi, M in enumerate(MS):
-                code = R.skinny_gemm_fp8_grouped(problems_of(M, sets[mi]))
+                code = R.skinny_gemm_fp8_grouped(problems_of(M, sets[mi]), flags)
                 if code != 0:
                     raise RuntimeError(f"grouped skinny GEMM returned {code}")
             return len(MS)
@@ -337,7 +337,7 @@ def run_gpu(args):
                 Aq, sa = act(M, K)
                 D = outs.setdefault((M, N), torch.empty((M, N), dtype=torch.bfloat16, device=dev))
                 one_list = [(Aq, c[0], sa, c[1], D) for c in copies]
-                us_g = _graph_time(torch, stream, lambda i: R.skinny_gemm_fp8_grouped(one_list), 2) / ncopies
+                us_g = _graph_time(torch, stream, lambda i: R.skinny_gemm_fp8_grouped(one_list, flags), 2) / ncopies
                 us_s = _graph_time(torch, stream, lambda i: R.skinny_gemm_fp8_tuned(Aq, copies[i % ncopies][0], sa, copies[0][1],
                                                                                     D, 0, 0, 0, flags), 24)
                 by = algo_bytes(M, N, K)
@@ -450,7 +450,8 @@ def run_gpu(args):
                                     "single": "one launch per GEMM, 20 per step"}[args.mode],
                    "l2": "inputs larger than L2: every GEMM of a step has its own weight matrix (1.09 GB per step) and "
                          "two such groups alternate, so a matrix is re-read only after 2.2 GB of other weights",
-                   "launch": "CUDA graph replay", "multi_gpu": "replicas only"},
+                   "launch": "CUDA graph replay, programmatic dependent launch (weights are never written in the timed region)",
+                   "multi_gpu": "replicas only"},
         "roofline": {"bound": "hbm", "achieved": per_gpu, "peak": peak, "unit": "GB/s", "frac": per_gpu / peak,
                      "traffic": TRAFFIC_PER_ALGO_BYTE[kernel] * step_bytes() / launches_per_step,
                      "traffic_note": TRAFFIC_NOTE[kernel],
@@ -840,6 +841,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-allreduce", action="store_true")
+    ap.add_argument("--no-overlap", action="store_true", help="plain launches instead of programmatic dependent launch")
     ap.add_argument("--no-suites", action="store_true", help="skip the compact dense / sparse / reduce / quantiser block")
     ap.add_argument("--mode", default="grouped", choices=["grouped", "layer", "single"],
                     help="launch shape of the headline sweep (the other two are reported beside it in `modes`)")

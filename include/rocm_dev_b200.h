@@ -156,6 +156,11 @@ int rdb_skinny_gemm_max_clusters(int M, int cluster_size, int smem_bytes);
  * (same return codes); count is 1..RDB_SKINNY_GROUP_MAX.  Results are
  * deterministic (a fixed K-order sum per shape list) but, K being cut at
  * different places, may differ from rdb_skinny_gemm_fp8's in the last bf16 bit.
+ *   - flags: 0, or RDB_SKINNY_OVERLAP_PRIOR_KERNEL (defined above): the launch
+ *     uses programmatic stream serialization - its CTAs take SMs as the preceding
+ *     kernel's CTAs leave and stream WEIGHTS while that kernel drains; activations,
+ *     scales, D and the workspace are touched only once it has completed.  Only
+ *     valid when no B of the list is written by the preceding kernel.
  *   - The problems must be independent: no D of the list may be an A or B of it.
  *   - Tiles shared by several CTAs are reduced through a per-device workspace
  *     (4.7 MiB, allocated on the first call): grouped calls on one device must
@@ -169,7 +174,7 @@ typedef struct rdb_skinny_problem {
     uint16_t *D;             /* [M,N] bf16, overwritten */
     int M, N, K, ldb;
 } rdb_skinny_problem;
-int rdb_skinny_gemm_fp8_grouped(const rdb_skinny_problem *problems, int count, void *stream);
+int rdb_skinny_gemm_fp8_grouped(const rdb_skinny_problem *problems, int count, unsigned flags, void *stream);
 
 /* The work split of a grouped call on `ctas` CTAs (pure host arithmetic, no
  * GPU): rows_per_unit[count] weight rows per streamed unit of each problem and

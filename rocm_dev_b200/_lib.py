@@ -33,7 +33,7 @@ _SIGNATURES = {
     "rdb_tuning_table_size": (i, []),
     "rdb_skinny_gemm_max_clusters": (i, [i, i, i]),
     "rdb_skinny_gemm_trace": (i, [vp, i, i]),
-    "rdb_skinny_gemm_fp8_grouped": (i, [vp, i, vp]),
+    "rdb_skinny_gemm_fp8_grouped": (i, [vp, i, C.c_uint, vp]),
     "rdb_skinny_gemm_grouped_plan": (i, [vp, i, i, vp, vp]),
     "rdb_skinny_gemm_grouped_trace": (i, [vp]),
     "rdb_skinny_gemm_fp8_tuned": (i, [u8p, u8p, f32p, f32p, vp, i, i, i, i, i, i, i, C.c_uint, vp]),

@@ -84,6 +84,7 @@ struct Params {
     int* status;
     unsigned long long* trace;              // optional [grid][4] %globaltimer stamps, else nullptr
     rdb::ar::PushTarget push;               // world > 0: the result goes, block-quantised, to the allreduce staging
+    int pdl;                                // launched with programmatic stream serialization (see the launcher)
 };
 
 __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
@@ -205,6 +206,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    if (p.pdl) pdl_launch_dependents();     // the next kernel of the stream may take SMs as this one's CTAs leave
 
     if (warp == 1) {
         // ---- producer: the CTA's whole unit range through the ring, never drained
@@ -212,7 +214,26 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
             const uint64_t pol_w = l2_policy_evict_first();   // weights are read once
             const uint64_t pol_a = l2_policy_evict_last();    // activations are re-read by every tile
             int pi = 0, last_pi = -1;
-            for (int u = lo, i = 0; u < hi; u++, i++) {
+            // Weights never depend on the preceding kernel: with programmatic launch the first ring of weight boxes
+            // is requested before waiting for that kernel to finish; the activations of those stages follow after.
+            const int pre = p.pdl ? (hi - lo < STAGES ? hi - lo : STAGES) : 0;
+            for (int pass = 0; pass < (p.pdl ? 2 : 0); pass++) {
+                int pj = 0;
+                if (pass == 1) pdl_wait_prior();
+                for (int i = 0; i < pre; i++) {
+                    int tile, kb;
+                    locate(p, lo + i, pj, tile, kb);
+                    const Problem& pr = p.prob[pj];
+                    const uint32_t dst = stage0 + i * STAGE;
+                    if (pass == 0) {
+                        mbar_arrive_expect_tx(full0 + 8 * i, static_cast<uint32_t>(pr.mpad + pr.R) * BK);
+                        tma_load_2d(dst + A_BYTES, &pr.tmW, kb * BK, tile * pr.R, full0 + 8 * i, pol_w);
+                    } else {
+                        tma_load_2d(dst, &pr.tmA, kb * BK, 0, full0 + 8 * i, pol_a);
+                    }
+                }
+            }
+            for (int u = lo + pre, i = pre; u < hi; u++, i++) {
                 const int s = i % STAGES;
                 const uint32_t ph = (i / STAGES) & 1;
                 if (i >= STAGES && !mbar_wait(empty0 + 8 * s, ph ^ 1)) { *abort_flag = 1; report_timeout(p.status); break; }
@@ -270,6 +291,9 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
     } else if ((warp & 3) == 0) {
         // ---- epilogue: warp 0 takes the even 32-column chunks of a tile, warp 4 the odd ones
         const int e = warp >> 2;
+        // everything the epilogue touches - the launch epoch, the workspace, the scales, D - may still belong to the
+        // preceding kernel until it has completed
+        if (p.pdl) pdl_wait_prior();
         const unsigned epoch = ld_acquire_gpu_u32(p.words);
         float* my_slot = p.partial + static_cast<size_t>(cta) * SLOT_FLOATS + lane * MAX_R;
         int pi = 0, seg = 0;
@@ -488,7 +512,9 @@ static void plan(const rdb_skinny_problem* pr, int count, int grid, int* R_out, 
 
 // `push`: nullptr for a plain grouped GEMM; else the one problem's result is delivered, block-quantised, to the
 // allreduce staging it describes (D is not written).
-static int run(const rdb_skinny_problem* pr, int count, cudaStream_t stream, const rdb::ar::PushTarget* push = nullptr) {
+static int run(const rdb_skinny_problem* pr, int count, cudaStream_t stream, const rdb::ar::PushTarget* push = nullptr,
+               unsigned flags = 0) {
+    if (flags & ~RDB_SKINNY_OVERLAP_PRIOR_KERNEL) return RDB_INVALID_CONFIG;
     if (!pr || count < 1 || count > kMaxProblems) return RDB_INVALID_CONFIG;
     if (push && (count != 1 || pr[0].N % 128 != 0)) return RDB_INVALID_CONFIG;
     long long units = 0;
@@ -551,12 +577,21 @@ static int run(const rdb_skinny_problem* pr, int count, cudaStream_t stream, con
     // A CTA that owns a shared tile waits for parts that HIGHER-numbered CTAs compute at the very start of their
     // ranges, so those CTAs must get onto the GPU: the cooperative launch makes the runtime guarantee it (and refuse
     // a grid that cannot be resident).  RDB_GROUPED_PLAIN_LAUNCH=1 selects a plain launch, for measurements.
+    // With RDB_SKINNY_OVERLAP_PRIOR_KERNEL the launch is a plain one with programmatic stream serialization instead:
+    // its CTAs take SMs as the preceding kernel's CTAs leave and stream weights while that kernel drains.
     static const bool plain_launch = [] { const char* v = getenv("RDB_GROUPED_PLAIN_LAUNCH"); return v && v[0] == '1'; }();
+    const bool pdl = (flags & RDB_SKINNY_OVERLAP_PRIOR_KERNEL) != 0;
+    prm.pdl = pdl ? 1 : 0;
     cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeCooperative;
-    attr[0].val.cooperative = 1;
+    if (pdl) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+    } else {
+        attr[0].id = cudaLaunchAttributeCooperative;
+        attr[0].val.cooperative = 1;
+    }
     cfg.attrs = attr;
-    cfg.numAttrs = plain_launch ? 0 : 1;
+    cfg.numAttrs = (plain_launch && !pdl) ? 0 : 1;
     if (cudaLaunchKernelEx(&cfg, skinny_grouped_kernel, prm) != cudaSuccess) {
         cudaGetLastError();
         return RDB_CUDA_ERROR;
@@ -569,8 +604,8 @@ static int run(const rdb_skinny_problem* pr, int count, cudaStream_t stream, con
 
 extern "C" {
 
-int rdb_skinny_gemm_fp8_grouped(const rdb_skinny_problem* problems, int count, void* stream) {
-    return rdb::grouped::run(problems, count, static_cast<cudaStream_t>(stream));
+int rdb_skinny_gemm_fp8_grouped(const rdb_skinny_problem* problems, int count, unsigned flags, void* stream) {
+    return rdb::grouped::run(problems, count, static_cast<cudaStream_t>(stream), nullptr, flags);
 }
 
 int rdb_skinny_gemm_fp8_allreduce_begin(void* ar_ctx, const rdb_skinny_problem* problem, void* stream) {

@@ -117,17 +117,19 @@ def _problem_array(problems):
     return arr
 
 
-def skinny_gemm_fp8_grouped(problems) -> int:
+def skinny_gemm_fp8_grouped(problems, flags: int = 0) -> int:
     """A list of independent skinny GEMMs in one persistent launch
     (rdb_skinny_gemm_fp8_grouped) - the shape of the reference's timed region,
     BATCH back-to-back ``skinny_gemm_fastpath`` calls on different weights
     (projects/skinny_gemm/bench.cu:51-60).  ``problems``: up to 32 tuples
     ``(A, B, scale_a, scale_b, D)`` of device tensors with the meaning of
-    ``skinny_gemm_fp8``.  Returns the status code."""
+    ``skinny_gemm_fp8``.  ``flags``: 0 or ``OVERLAP_PRIOR_KERNEL`` (the launch may
+    start streaming weights while the preceding kernel of the stream drains).
+    Returns the status code."""
     dev = problems[0][0].device
     arr = _problem_array(problems)
     with torch.cuda.device(dev):
-        return int(lib().rdb_skinny_gemm_fp8_grouped(arr, len(problems), _stream_ptr(dev)))
+        return int(lib().rdb_skinny_gemm_fp8_grouped(arr, len(problems), flags, _stream_ptr(dev)))
 
 
 def skinny_gemm_grouped_plan(shapes, ctas: int = 148):

@@ -168,6 +168,30 @@ def test_grouped_whole_sweep_is_deterministic_and_replayable(cuda_device, oracle
             torch.cuda.synchronize()
             assert all(torch.equal(a, p[4]) for a, p in zip(first, problems))
     assert R.lib().rdb_device_status() == 0
+    # programmatic launch: each launch streams weights while the one before drains; four in a row, with a plain
+    # per-GEMM launch in between, leave the same bits
+    for p in problems:
+        p[4].zero_()
+    for i in range(4):
+        assert R.skinny_gemm_fp8_grouped(problems, flags=R.OVERLAP_PRIOR_KERNEL) == 0
+        if i == 1:
+            R.skinny_gemm_fp8(problems[0][0], problems[0][1], problems[0][2], problems[0][3])
+    torch.cuda.synchronize()
+    assert R.lib().rdb_device_status() == 0
+    assert all(torch.equal(a, p[4]) for a, p in zip(first, problems))
+    with torch.cuda.stream(stream):
+        g2 = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g2, stream=stream):
+            for _ in range(3):             # the same list each time: the K split, and so the bits, depend on the list
+                assert R.skinny_gemm_fp8_grouped(problems, flags=R.OVERLAP_PRIOR_KERNEL) == 0
+        for p in problems:
+            p[4].zero_()
+        g2.replay()
+        g2.replay()
+        torch.cuda.synchronize()
+    assert all(torch.equal(a, p[4]) for a, p in zip(first, problems))
+    assert R.lib().rdb_device_status() == 0
+    assert R.lib().rdb_skinny_gemm_fp8_grouped(None, 1, 2, 0) == 6          # unknown flag
 
 
 def test_grouped_matches_the_plan_and_rejects_bad_lists(cuda_device):
@@ -181,16 +205,16 @@ def test_grouped_matches_the_plan_and_rejects_bad_lists(cuda_device):
     x = torch.zeros(4096, dtype=torch.uint8, device=cuda_device)
     f = torch.ones(1, device=cuda_device)
     ok = SkinnyProblem(x.data_ptr(), x.data_ptr(), f.data_ptr(), f.data_ptr(), x.data_ptr(), 8, 16, 64, 64)
-    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(ok), 0, 0) == 6
-    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(ok), 33, 0) == 6
+    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(ok), 0, 0, 0) == 6
+    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(ok), 33, 0, 0) == 6
     bad = SkinnyProblem(x.data_ptr(), x.data_ptr(), f.data_ptr(), f.data_ptr(), x.data_ptr(), 33, 16, 64, 64)
-    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(bad), 1, 0) == 1
+    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(bad), 1, 0, 0) == 1
     bad = SkinnyProblem(x.data_ptr(), x.data_ptr(), f.data_ptr(), f.data_ptr(), x.data_ptr(), 8, 15, 64, 64)
-    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(bad), 1, 0) == 2
+    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(bad), 1, 0, 0) == 2
     bad = SkinnyProblem(x.data_ptr(), x.data_ptr(), f.data_ptr(), f.data_ptr(), x.data_ptr(), 8, 16, 40, 48)
-    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(bad), 1, 0) == 3
+    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(bad), 1, 0, 0) == 3
     bad = SkinnyProblem(x.data_ptr() + 1, x.data_ptr(), f.data_ptr(), f.data_ptr(), x.data_ptr(), 8, 16, 64, 64)
-    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(bad), 1, 0) == 7
+    assert L.rdb_skinny_gemm_fp8_grouped(C.byref(bad), 1, 0, 0) == 7
 
 
 def test_row_pitch_and_output_overwrite(cuda_device, oracle):
