@@ -933,7 +933,10 @@ int rdb_ar_create(int rank, int world, void* const* workspaces, size_t max_elems
     // The epoch restarts at zero, so flag words left by an earlier context over the same workspace must
     // go: this rank's flag block is cleared here.  Creation is a collective set-up step - no rank may
     // start a call before every rank's rdb_ar_create has returned.
-    if (cudaMemset(c->ws[rank] + c->L.off_flags, 0, 1024) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+    // ... and so must the line area, whose valid marks are epochs too (a line left by an earlier context's call of
+    // the same number would otherwise pass for this context's).
+    if (cudaMemset(c->ws[rank] + c->L.off_ll, 0, c->L.off_flags + 1024 - c->L.off_ll) != cudaSuccess ||
+        cudaDeviceSynchronize() != cudaSuccess) {
         cudaGetLastError();
         delete c;
         return RDB_CUDA_ERROR;

@@ -199,6 +199,36 @@ def test_automatic_choice_at_the_one_shot_limit(cuda_device, oracle, world):
         lr.close()
 
 
+@pytest.mark.gpu
+def test_a_second_context_over_a_used_workspace(cuda_device, oracle):
+    """Epochs restart with a new context: what earlier calls left in the workspace (flag words, lines whose valid
+    mark is an epoch) must not pass for the new context's calls of the same number."""
+    import rocm_dev_b200 as R
+    from rocm_dev_b200.allreduce import _create
+    world, n = 2, 128 * 33
+    lr = R.LocalRanks(world, max_elems=1 << 16, device=cuda_device)
+    try:
+        def run(seed, algo):
+            xs = [torch.randn(n, generator=torch.Generator().manual_seed(seed + r)).bfloat16() for r in range(world)]
+            outs = lr.all_reduce([x.to(cuda_device) for x in xs], algo=algo)
+            torch.cuda.synchronize()
+            want, _, _ = oracle.allreduce_fp8(np.stack([_bits(x) for x in xs]))
+            return all(np.array_equal(_bits(o), want) for o in outs)
+        for algo in (1, 2, 1, 2):
+            assert run(10 * algo, algo)
+        torch.cuda.synchronize()
+        for c in lr.ctx:
+            R.lib().rdb_ar_destroy(c)
+        with torch.cuda.device(cuda_device):
+            ptrs = [w.ptr for w in lr.ws]
+            lr.ctx = [_create(r, world, ptrs, 1 << 16) for r in range(world)]       # epochs are back at zero
+        for algo in (1, 2, 1, 2):
+            assert run(100 + 7 * algo, algo)                                          # different data, same call numbers
+        assert R.lib().rdb_device_status() == 0
+    finally:
+        lr.close()
+
+
 def test_regather_variant_oracle_properties(oracle):
     """The FP8-all-gather variant is decode(encode(first variant)): idempotent
     (a second round trip changes nothing), exact on zero blocks, and within one
