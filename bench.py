@@ -508,6 +508,47 @@ def allreduce_parity(torch, dist, R, ar, reg, dev, rank, world):
             "ranks": world}
 
 
+def allreduce_graph_parity(torch, dist, arg, regg, dev, rank, world, so_far):
+    """The oracle check for calls recorded in a CUDA graph: per size one graph of three calls (automatic into the
+    registered buffer, two-shot into an ordinary buffer, second variant), replayed three times with new inputs."""
+    import numpy as np
+    from oracle import oracle as O
+    bits = lambda t: t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)  # noqa: E731
+    cases, bad = 0, 0
+    for T in (16, 1024):
+        n = T * 8192
+        x = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        y2, y3 = torch.empty_like(x), torch.empty_like(x)
+
+        def issue():
+            arg.all_reduce(x, out=regg[:n])
+            arg.all_reduce(x, out=y2, algo=2)
+            arg.all_reduce(x, out=y3, algo=3)
+        issue()
+        torch.cuda.synchronize()
+        dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            issue()
+        for rep in range(3):
+            xs = [torch.randn(n, generator=torch.Generator().manual_seed(500 + 10 * rep + r + T)).bfloat16() for r in range(world)]
+            x.copy_(xs[rank])
+            g.replay()
+            torch.cuda.synchronize()
+            stacked = np.stack([bits(v) for v in xs])
+            want = O.allreduce_fp8(stacked)[0]
+            bad += int((bits(regg[:n]) != want).sum()) + int((bits(y2) != want).sum())
+            bad += int((bits(y3) != O.allreduce_fp8_regather(stacked)).sum())
+            cases += 3
+            dist.barrier()
+        del g
+    t = torch.tensor([bad], dtype=torch.int64, device=dev)
+    dist.all_reduce(t)
+    total = int(t.item())
+    return {"bit_exact": so_far["bit_exact"] and total == 0, "cases": so_far["cases"] + cases,
+            "graph_replay_cases": cases, "mismatching_elements": so_far["mismatching_elements"] + total}
+
+
 def bench_allreduce(torch, dist, R, dev, rank, world):
     """FP8-encoded allreduce against NCCL's bf16 allreduce on [T, 8192] bf16
     tensors.  busBW = S/t * 2(n-1)/n with S the bf16 size; device time, max over
@@ -540,12 +581,37 @@ def bench_allreduce(torch, dist, R, dev, rank, world):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.median().item()) * 1e-3
 
+    # the same calls recorded in a CUDA graph (a context that counts its calls on the device) and replayed: what a
+    # graph-captured decode loop sees, without the per-call host path; NCCL's allreduce recorded the same way beside it
+    arg = R.Fp8AllReduce(max_elems=4096 * 8192, backend="ipc", capturable=True)
+    regg = arg.new_result_buffer(4096 * 8192)
+
+    out["parity"].update(allreduce_graph_parity(torch, dist, arg, regg, dev, rank, world, out["parity"]))
+
+    def timed_graph(fn, iters):
+        try:
+            fn()
+            torch.cuda.synchronize()
+            dist.barrier()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                for _ in range(iters):
+                    fn()
+            t = timed(g.replay, 2) / iters
+            del g
+            return t
+        except Exception as e:  # noqa: BLE001 - a collective library that cannot be captured here
+            out.setdefault("graph_errors", []).append(f"{type(e).__name__}: {e}"[:160])
+            return None
+
     for T in (1, 16, 128, 1024, 4096):
         n = T * 8192
         x = torch.randn(n, generator=torch.Generator(device=dev).manual_seed(rank), device=dev).bfloat16()
         y = torch.empty_like(x)
         z = x.clone()
         iters = 40 if T <= 128 else 10
+        t_graph = timed_graph(lambda: arg.all_reduce(x, out=regg[:n]), iters)
+        t_nccl_graph = timed_graph(lambda: dist.all_reduce(z), iters) if os.environ.get("RDB_BENCH_NCCL_GRAPH", "1") == "1" else None
         t_fp8 = timed(lambda: ar.all_reduce(x, out=y), iters)           # result into an ordinary buffer of the caller
         t_reg = timed(lambda: ar.all_reduce(x, out=reg[:n]), iters)     # result into the caller's registered buffer
         t_nccl = timed(lambda: dist.all_reduce(z), iters)
@@ -561,9 +627,13 @@ def bench_allreduce(torch, dist, R, dev, rank, world):
                                  "fp8_busbw": round(S / t_fp8 * f / 1e9, 1), "nccl_bf16_busbw": round(S / t_nccl * f / 1e9, 1),
                                  "ratio": round(t_nccl / t_fp8, 3),
                                  "fp8_gather_variant_us": round(t_v2 * 1e6, 2), "fp8_gather_variant_busbw": round(S / t_v2 * f / 1e9, 1),
-                                 "fp8_gather_variant_ratio": round(t_nccl / t_v2, 3)}
+                                 "fp8_gather_variant_ratio": round(t_nccl / t_v2, 3),
+                                 "fp8_graph_us": round(t_graph * 1e6, 2) if t_graph else None,
+                                 "nccl_bf16_graph_us": round(t_nccl_graph * 1e6, 2) if t_nccl_graph else None,
+                                 "graph_ratio": round(t_nccl_graph / t_graph, 3) if t_graph and t_nccl_graph else None}
     if R.lib().rdb_device_status() != 0:
         out["error"] = "device status word reports a timed-out wait"
+    arg.close()
     ar.close()
     return out
 

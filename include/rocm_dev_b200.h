@@ -333,6 +333,19 @@ int rdb_ar_set_multicast(void *ctx, void *multicast_workspace);
  * Same result bits.  NULL unregisters.  Like rdb_ar_result, the buffer must not
  * be read by work queued after this rank's NEXT call. */
 int rdb_ar_register_buffers(void *ctx, void *const *buffers, size_t bytes);
+/* Optional, before the context's first call and on every rank alike: count the
+ * calls on the device (a word of the own workspace that the last block of each
+ * call advances) instead of on the host.  rdb_ar_allreduce and
+ * rdb_skinny_gemm_fp8_allreduce launches then carry nothing that changes from
+ * call to call, so they may be recorded in a CUDA graph (stream capture) and
+ * replayed - with the buffers they were recorded with - any number of times,
+ * mixed with direct calls.  All calls of such a context must be ordered among
+ * themselves (one stream, or graph / event dependencies), and every rank must
+ * issue the same sequence.  Make one call before the first capture (per-device
+ * set-up allocates).  rdb_ar_phase / rdb_ar_begin_call are refused
+ * (RDB_INVALID_CONFIG, -1) on such a context.  Returns RDB_INVALID_CONFIG once a
+ * call has been issued. */
+int rdb_ar_set_device_epoch(void *ctx, int on);
 /* Diagnostics: registers a device buffer of 16 uint64.  While registered, each
  * rdb_ar_allreduce call stores %globaltimer stamps of its first CTA in words
  * 0-5 (entry, own pushes issued, all ranks' pushes arrived, own reduction and

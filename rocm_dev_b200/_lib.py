@@ -62,6 +62,7 @@ _SIGNATURES = {
     "rdb_ar_set_multicast": (i, [vp, vp]),
     "rdb_ar_set_trace": (i, [vp, vp]),
     "rdb_ar_register_buffers": (i, [vp, C.POINTER(C.c_void_p), C.c_size_t]),
+    "rdb_ar_set_device_epoch": (i, [vp, i]),
     "rdb_ar_allreduce": (i, [vp, vp, vp, C.c_size_t, i, vp]),
     "rdb_ar_result": (C.c_void_p, [vp]),
     "rdb_skinny_gemm_fp8_allreduce": (i, [vp, vp, vp, vp]),

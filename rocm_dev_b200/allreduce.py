@@ -81,9 +81,15 @@ class Fp8AllReduce:
     workspace is a torch symmetric-memory allocation (needs an NCCL group);
     if the allocation has an NVLS multicast address the bf16 all-gather uses
     multimem stores.  backend="auto" tries "symm" and falls back to "ipc".
+
+    capturable=True (every rank alike): the calls are counted on the device
+    (rdb_ar_set_device_epoch), so ``all_reduce`` and ``skinny_gemm_all_reduce``
+    may be recorded under ``torch.cuda.graph`` and replayed; make one call
+    before the first capture and keep all calls of the object stream-ordered.
     """
 
-    def __init__(self, max_elems: int, group=None, device=None, backend: str = "ipc", multimem: bool | None = None):
+    def __init__(self, max_elems: int, group=None, device=None, backend: str = "ipc", multimem: bool | None = None,
+                 capturable: bool = False):
         import torch.distributed as dist
         self.group = group
         self.rank = dist.get_rank(group)
@@ -110,6 +116,9 @@ class Fp8AllReduce:
                 ptrs = self._ipc_workspace(dist)
             self.backend = "symm" if self.symm is not None else "ipc"
             self.ctx = _create(self.rank, self.world, ptrs, self.max_elems)
+            self.capturable = bool(capturable)
+            if self.capturable:
+                check(lib().rdb_ar_set_device_epoch(self.ctx, 1), "rdb_ar_set_device_epoch")
             if multimem is None:
                 # one multicast store replaces W-1 peer stores: measured slower than per-peer stores at 2
                 # and 4 ranks, 1.5 % faster at 8 ranks for 64 MiB but twice as slow there for 16 MiB with a

@@ -112,6 +112,8 @@ struct Ctx {
     uint8_t* reg[kMaxWorld];   // optional: every rank's registered result buffer (rank order), else nullptr
     size_t reg_bytes;
     unsigned epoch;
+    bool device_epoch;    // calls are counted by the kernels (a word of the own workspace), not by the host
+    unsigned long long calls;   // calls issued so far, in either mode
     int push_order;       // 0 linear, 1 rotated by rank, 2 owner-interleaved (default)
     unsigned long long* trace;   // optional: 8 globaltimer stamps of the last fused call (diagnostics)
     size_t pending_n;     // a call opened by begin_prepushed and not yet finished (0: none)
@@ -125,7 +127,8 @@ struct KParams {
     int rank, world;
     size_t n;            // elements (multiple of 128)
     size_t groups;       // ceil(n / 512)
-    unsigned epoch;
+    unsigned epoch;      // the call's number when the host counts (epoch_dev == nullptr)
+    unsigned* epoch_dev; // device-side counting: [0] completed calls of this context, [1] blocks done in the running call
     int one_shot;
     int fp8_gather;      // two-shot only: the all-gather carries re-encoded FP8 blocks instead of bf16
     int lines;           // the encoded groups travel as self-validating 128-byte lines (no flag hand-over before the reduction)
@@ -233,7 +236,7 @@ __device__ __forceinline__ uint4 regroup16(const uint2* q, int lane) {
 // a result that was never written.  Publishing at the end of the producer - not
 // at the start of the consumer - means a consumer launch never depends on a
 // launch issued after it.
-__device__ __forceinline__ void publish_when_grid_done(const KParams& p, int which, bool failed) {
+__device__ __forceinline__ void publish_when_grid_done(const KParams& p, const unsigned ep, int which, bool failed) {
     __syncthreads();
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
@@ -243,7 +246,7 @@ __device__ __forceinline__ void publish_when_grid_done(const KParams& p, int whi
             // one atomic it needs anyway.  No further fence before the flag stores: every block fenced its own stores
             // before counting itself, the last block's atomic observes all those counts, and st.release orders the
             // flag after everything that happened before it.
-            unsigned* cnt = reinterpret_cast<unsigned*>(p.ws[p.rank] + p.L.off_flags) + 64 + which * 2 + (p.epoch & 1u);   // two calls may be in flight
+            unsigned* cnt = reinterpret_cast<unsigned*>(p.ws[p.rank] + p.L.off_flags) + 64 + which * 2 + (ep & 1u);   // two calls may be in flight
             __threadfence_system();
             const unsigned old = atomicAdd(cnt, failed ? 0x10001u : 1u);
             if ((old & 0xFFFFu) == gridDim.x - 1) {
@@ -255,8 +258,8 @@ __device__ __forceinline__ void publish_when_grid_done(const KParams& p, int whi
         __syncwarp();
         // one lane per peer: the W release stores travel concurrently
         if (word && lane < p.world) {
-            unsigned* f = reinterpret_cast<unsigned*>(p.ws[lane] + p.L.off_flags) + (which * 2 + (p.epoch & 1u)) * kMaxWorld + p.rank;
-            st_release_sys(f, (p.epoch << 1) | (word & 1u));
+            unsigned* f = reinterpret_cast<unsigned*>(p.ws[lane] + p.L.off_flags) + (which * 2 + (ep & 1u)) * kMaxWorld + p.rank;
+            st_release_sys(f, (ep << 1) | (word & 1u));
         }
     }
 }
@@ -266,26 +269,26 @@ __device__ __forceinline__ void publish_when_grid_done(const KParams& p, int whi
 // r's word, so the W acquire loads overlap.  Returns true when every rank
 // arrived and none of them reported a failure; otherwise the status word gets
 // RDB_DEVICE_TIMEOUT (the own wait ran out, or a peer's did and it said so).
-__device__ __forceinline__ bool wait_flags(const KParams& p, int which) {
+__device__ __forceinline__ bool wait_flags(const KParams& p, const unsigned ep, int which) {
     __shared__ int ok_s;
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
         // one flag row per epoch parity: two calls may be in flight and may finish out of order,
         // but calls of equal parity are ordered, so each word only ever grows
-        const unsigned* mine = reinterpret_cast<const unsigned*>(p.ws[p.rank] + p.L.off_flags) + (which * 2 + (p.epoch & 1u)) * kMaxWorld;
+        const unsigned* mine = reinterpret_cast<const unsigned*>(p.ws[p.rank] + p.L.off_flags) + (which * 2 + (ep & 1u)) * kMaxWorld;
         bool ok = true;
         if (lane < p.world) {
             // epochs only grow; a flag at or beyond this call's epoch means "arrived"
             unsigned v = ld_acquire_sys(mine + lane);
-            if (static_cast<int>((v >> 1) - p.epoch) < 0) {
+            if (static_cast<int>((v >> 1) - ep) < 0) {
                 // not there yet: only now read the clock and the budget (a global load that must stay off the fast path)
                 const uint64_t t0 = globaltimer_ns(), budget = wait_budget_ns();
                 unsigned spins = 0;
-                while (static_cast<int>(((v = ld_acquire_sys(mine + lane)) >> 1) - p.epoch) < 0) {
+                while (static_cast<int>(((v = ld_acquire_sys(mine + lane)) >> 1) - ep) < 0) {
                     if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > budget) { ok = false; break; }
                 }
             }
-            if (ok && (v >> 1) == p.epoch && (v & 1u)) ok = false;   // that rank gave up before delivering
+            if (ok && (v >> 1) == ep && (v & 1u)) ok = false;   // that rank gave up before delivering
         }
         ok = __all_sync(0xffffffffu, ok);
         if (lane == 0) {
@@ -295,6 +298,26 @@ __device__ __forceinline__ bool wait_flags(const KParams& p, int which) {
     }
     __syncthreads();
     return ok_s != 0;
+}
+
+// The number of the call a kernel belongs to.  Ordinarily the host counts the calls and passes the number; a context
+// switched to device-side counting (rdb_ar_set_device_epoch) keeps the count of completed calls in a word of its own
+// workspace instead, so that a launch recorded once in a CUDA graph finds the right number on every replay.  The last
+// block to finish a call stores the new count - after every block of the grid has read the old one, since a block
+// counts itself only when it is done.
+__device__ __forceinline__ unsigned call_epoch(const KParams& p) {
+    return p.epoch_dev ? *reinterpret_cast<volatile unsigned*>(p.epoch_dev) + 1u : p.epoch;
+}
+__device__ __forceinline__ void call_done(const KParams& p, const unsigned ep) {
+    if (p.epoch_dev == nullptr) return;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        unsigned* done = p.epoch_dev + 1;
+        if (atomicAdd(done, 1u) == gridDim.x - 1) {
+            *done = 0;
+            *reinterpret_cast<volatile unsigned*>(p.epoch_dev) = ep;
+        }
+    }
 }
 
 // ------------------------------------------------ flag-in-line transport
@@ -307,8 +330,8 @@ __device__ __forceinline__ uint4 ld_line16(const void* addr) {
     return v;
 }
 // Slot of (source rank, position) in the line area of a workspace, for this call's parity.
-__device__ __forceinline__ uint8_t* line_slot(const KParams& p, uint8_t* ws, int src_rank, size_t slot_g) {
-    return ws + p.L.off_ll + ((static_cast<size_t>(p.epoch & 1u) * p.world + src_rank) * p.L.slot_groups + slot_g) * kLlGroupBytes;
+__device__ __forceinline__ uint8_t* line_slot(const KParams& p, const unsigned ep, uint8_t* ws, int src_rank, size_t slot_g) {
+    return ws + p.L.off_ll + ((static_cast<size_t>(ep & 1u) * p.world + src_rank) * p.L.slot_groups + slot_g) * kLlGroupBytes;
 }
 
 // What the two store instructions of a group carry, per lane: `a` goes to line lane / 8, position lane % 8; `b`
@@ -409,7 +432,7 @@ __device__ __forceinline__ bool push_item(const KParams& p, size_t it, size_t ro
     return true;
 }
 
-__device__ __forceinline__ void push_body(const KParams& p) {
+__device__ __forceinline__ void push_body(const KParams& p, const unsigned ep) {
     const int lane = threadIdx.x & 31;
     const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
     const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
@@ -440,18 +463,18 @@ __device__ __forceinline__ void push_body(const KParams& p) {
             for (int h = 0; h < 2; h++) q[h] = encode8(in[h], s[h]);
             // the four block scales of the group: (half 0: lanes 0, 16), (half 1: lanes 0, 16)
             const float s1 = __shfl_sync(0xffffffffu, s[0], 16), s3 = __shfl_sync(0xffffffffu, s[1], 16);
-            const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + p.rank) * p.L.slot_groups + cur.slot_g;
+            const size_t slot = (static_cast<size_t>(ep & 1u) * p.world + p.rank) * p.L.slot_groups + cur.slot_g;
             if (p.lines) {
                 const float s0b = __shfl_sync(0xffffffffu, s[0], 0), s2b = __shfl_sync(0xffffffffu, s[1], 0);
                 uint4 la, lb;
-                lines_of_group(q, s0b, s1, s2b, s3, p.epoch, lane, la, lb);
+                lines_of_group(q, s0b, s1, s2b, s3, ep, lane, la, lb);
                 for (int k = cur.first; k <= cur.last; k++) {
                     int peer = k;
                     if (p.one_shot) {                      // start after myself: the remote lines leave first
                         peer = p.rank + 1 + k;
                         if (peer >= p.world) peer -= p.world;
                     }
-                    uint8_t* dst = line_slot(p, p.ws[peer], p.rank, cur.slot_g);
+                    uint8_t* dst = line_slot(p, ep, p.ws[peer], p.rank, cur.slot_g);
                     st_line16(dst + (lane >> 3) * 128 + (lane & 7) * 16, la);
                     if (lane < 8) st_line16(dst + 4 * 128 + lane * 16, lb);
                 }
@@ -479,14 +502,14 @@ __device__ __forceinline__ void push_body(const KParams& p) {
 }
 
 __global__ void __launch_bounds__(kThreads) ar_push_kernel(const KParams p) {
-    push_body(p);
-    if (!p.lines) publish_when_grid_done(p, 0, false);
+    push_body(p, p.epoch);
+    if (!p.lines) publish_when_grid_done(p, p.epoch, 0, false);
 }
 
 // ------------------------------------------------------------------ phase 2
 // Returns false if a group's lines did not arrive within the budget (line transport only; with the flag-guarded
 // staging the caller has already waited and passes `arrived`).
-__device__ __forceinline__ bool reduce_body(const KParams& p, bool arrived) {
+__device__ __forceinline__ bool reduce_body(const KParams& p, const unsigned ep, bool arrived) {
     const int lane = threadIdx.x & 31;
     const size_t warp = (blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x) >> 5;
     const size_t nwarps = (gridDim.x * static_cast<size_t>(blockDim.x)) >> 5;
@@ -506,9 +529,9 @@ __device__ __forceinline__ bool reduce_body(const KParams& p, bool arrived) {
             uint2 q0, q1;
             float s0, s1;
             if (p.lines) {
-                if (!fetch_lines(line_slot(p, mine, r, slot_g), p.epoch, lane, q0, q1, s0, s1)) { ok = false; break; }
+                if (!fetch_lines(line_slot(p, ep, mine, r, slot_g), ep, lane, q0, q1, s0, s1)) { ok = false; break; }
             } else {
-                const size_t slot = (static_cast<size_t>(p.epoch & 1u) * p.world + r) * p.L.slot_groups + slot_g;
+                const size_t slot = (static_cast<size_t>(ep & 1u) * p.world + r) * p.L.slot_groups + slot_g;
                 const uint2* src = reinterpret_cast<const uint2*>(mine + p.L.off_q + slot * kGroup) + lane;
                 q0 = __ldcg(src);
                 q1 = __ldcg(src + 32);
@@ -588,11 +611,13 @@ __device__ __forceinline__ bool reduce_body(const KParams& p, bool arrived) {
 }
 
 __global__ void __launch_bounds__(kThreads) ar_reduce_kernel(const KParams p) {
-    const bool arrived = p.lines ? true : wait_flags(p, 0);       // lines are waited for group by group
-    const bool reduced = reduce_body(p, arrived);
+    const unsigned ep = call_epoch(p);
+    const bool arrived = p.lines ? true : wait_flags(p, ep, 0);       // lines are waited for group by group
+    const bool reduced = reduce_body(p, ep, arrived);
     // also after a timeout, so that peers are not left waiting - with the failure bit set, so that
     // they do not take the missing shard for delivered
-    if (!p.one_shot) publish_when_grid_done(p, 1, !arrived || !reduced);
+    if (!p.one_shot) publish_when_grid_done(p, ep, 1, !arrived || !reduced);
+    call_done(p, ep);                  // the closing launch of a GEMM + allreduce call on a context that counts on the device
 }
 
 // ------------------------------------------------------------------ phase 3
@@ -628,7 +653,7 @@ __device__ __forceinline__ void copy_out_body(const KParams& p) {
 }
 
 __global__ void __launch_bounds__(kThreads) ar_gather_kernel(const KParams p) {
-    if (!wait_flags(p, 1)) return;
+    if (!wait_flags(p, p.epoch, 1)) return;
     copy_out_body(p);
 }
 
@@ -650,33 +675,38 @@ __device__ __forceinline__ void stamp(const KParams& p, int slot) {
 }
 
 __global__ void __launch_bounds__(kThreads, kBlocksPerSm) ar_fused_kernel(const KParams p) {
+    const unsigned ep = call_epoch(p);
     stamp(p, 0);
-    push_body(p);
+    push_body(p, ep);
     stamp(p, 1);
     bool arrived = true;
     if (!p.lines) {                    // flag-guarded staging: one hand-over before the reduction
-        publish_when_grid_done(p, 0, false);
-        arrived = wait_flags(p, 0);
+        publish_when_grid_done(p, ep, 0, false);
+        arrived = wait_flags(p, ep, 0);
     }
     stamp(p, 2);
-    const bool reduced = reduce_body(p, arrived);
+    const bool reduced = reduce_body(p, ep, arrived);
     stamp(p, 3);
-    if (p.one_shot) return;
-    publish_when_grid_done(p, 1, !arrived || !reduced);
-    const bool gathered = wait_flags(p, 1);
-    stamp(p, 4);
-    if (gathered) copy_out_body(p);
-    stamp(p, 5);
+    if (!p.one_shot) {
+        publish_when_grid_done(p, ep, 1, !arrived || !reduced);
+        const bool gathered = wait_flags(p, ep, 1);
+        stamp(p, 4);
+        if (gathered) copy_out_body(p);
+        stamp(p, 5);
+    }
+    call_done(p, ep);
 }
 
 // One-shot call over the line transport: a warp pushes its groups, then reduces the same groups as the lines of all
 // ranks arrive.  No block waits for another block of this grid, so the launch is an ordinary one of any size.
 __global__ void __launch_bounds__(kThreads) ar_oneshot_lines_kernel(const KParams p) {
+    const unsigned ep = call_epoch(p);
     stamp(p, 0);
-    push_body(p);
+    push_body(p, ep);
     stamp(p, 1);
-    reduce_body(p, true);
+    reduce_body(p, ep, true);
     stamp(p, 3);
+    call_done(p, ep);
 }
 
 // Standalone encoder (the quantise step alone, for bit-exact tests and callers
@@ -749,6 +779,9 @@ static int fused_blocks_per_sm() {
     return cached;
 }
 
+// The two words of the own flag block that hold the device-side call count and its block counter.
+static unsigned* epoch_words(Ctx* c) { return reinterpret_cast<unsigned*>(c->ws[c->rank] + c->L.off_flags) + 96; }
+
 static int grid_for(size_t warps_needed, int sm_count, int blocks_per_sm = kBlocksPerSm) {
     size_t blocks = (warps_needed * 32 + kThreads - 1) / kThreads;
     const size_t cap = static_cast<size_t>(sm_count) * blocks_per_sm;
@@ -773,6 +806,7 @@ static int run_phase(Ctx* c, int phase, const uint16_t* x, uint16_t* out, size_t
     p.n = n;
     p.groups = (n + kGroup - 1) / kGroup;
     p.epoch = epoch;
+    p.epoch_dev = (c->device_epoch && (phase == 0 || prepushed)) ? epoch_words(c) : nullptr;
     p.one_shot = algo == 1 ? 1 : 0;
     p.fp8_gather = algo == 3 ? 1 : 0;
     p.push_order = c->push_order;
@@ -857,6 +891,8 @@ int begin_prepushed(void* ctx, size_t n, PushTarget* t) {
     t->rank = c->rank;
     t->world = c->world;
     t->epoch = ++c->epoch;
+    t->epoch_dev = c->device_epoch ? epoch_words(c) : nullptr;
+    c->calls++;
     c->pending_n = n;
     c->pending_epoch = t->epoch;
     return RDB_SUCCESS;
@@ -867,6 +903,7 @@ void cancel_prepushed(void* ctx) {
     if (c && c->pending_n != 0) {
         c->pending_n = 0;
         c->epoch--;
+        c->calls--;
     }
 }
 
@@ -927,6 +964,8 @@ int rdb_ar_create(int rank, int world, void* const* workspaces, size_t max_elems
     for (int i = 0; i < rdb::ar::kMaxWorld; i++) c->reg[i] = nullptr;
     c->reg_bytes = 0;
     c->epoch = 0;
+    c->device_epoch = false;
+    c->calls = 0;
     c->pending_n = 0;
     c->pending_epoch = 0;
     c->trace = nullptr;
@@ -996,12 +1035,22 @@ int rdb_ar_allreduce(void* ctx, const uint16_t* x, uint16_t* out, size_t n, int 
     const unsigned epoch = ++c->epoch;
     r = run_phase(c, 0, x, out, n, algo, epoch, static_cast<cudaStream_t>(stream));   // 0 = all phases in one launch
     if (r != RDB_SUCCESS) c->epoch--;    // nothing was launched: the ranks' epochs stay in step
+    else c->calls++;
     return r;
+}
+
+int rdb_ar_set_device_epoch(void* ctx, int on) {
+    rdb::ar::Ctx* c = static_cast<rdb::ar::Ctx*>(ctx);
+    if (!c) return RDB_INVALID_CONFIG;
+    if (c->calls != 0 || c->epoch != 0) return RDB_INVALID_CONFIG;    // the two counts would disagree from here on
+    c->device_epoch = on != 0;
+    return RDB_SUCCESS;
 }
 
 int rdb_ar_begin_call(void* ctx) {
     rdb::ar::Ctx* c = static_cast<rdb::ar::Ctx*>(ctx);
-    if (!c) return -1;
+    if (!c || c->device_epoch) return -1;       // the separate phases take their call number from the host
+    c->calls++;
     return static_cast<int>(++c->epoch);
 }
 
@@ -1009,7 +1058,7 @@ int rdb_ar_phase(void* ctx, int phase, int epoch, const uint16_t* x, uint16_t* o
     rdb::ar::Ctx* c = static_cast<rdb::ar::Ctx*>(ctx);
     int r = rdb::ar::check_call(c, x, out, n, algo);
     if (r != RDB_SUCCESS) return r;
-    if (phase < 1 || phase > 3 || epoch < 1) return RDB_INVALID_CONFIG;
+    if (phase < 1 || phase > 3 || epoch < 1 || c->device_epoch) return RDB_INVALID_CONFIG;
     return rdb::ar::run_phase(c, phase, x, out, n, algo, static_cast<unsigned>(epoch), static_cast<cudaStream_t>(stream));
 }
 

@@ -15,7 +15,8 @@ struct PushTarget {
     uint8_t* ws[8];            // every rank's workspace, rank order
     size_t off_q, off_s, off_flags, slot_groups;
     int rank, world;           // world == 0: no delivery (plain GEMM)
-    unsigned epoch;
+    unsigned epoch;            // the call's number when the host counts the calls ...
+    const unsigned* epoch_dev; // ... else the device word holding the number of completed calls (this call: that + 1)
 };
 
 // Opens a one-shot call on `ctx` whose encoded input another kernel delivers:

@@ -129,18 +129,25 @@ __device__ __forceinline__ void store_chunk(const Problem& pr, const float* v, f
     }
 }
 
+// The number of the allreduce call a fused launch feeds: passed by the host, or - on a context that counts its calls on
+// the device, so that the launch can be replayed from a CUDA graph - one more than the count of completed calls, which
+// only the closing reduce launch of the same call advances.
+__device__ __forceinline__ unsigned push_call_number(const rdb::ar::PushTarget& t) {
+    return t.epoch_dev ? *reinterpret_cast<const volatile unsigned*>(t.epoch_dev) + 1u : t.epoch;
+}
+
 // GEMM -> allreduce fusion: one finished 128-column block of output row m (bf16
 // values packed two per word, their maximum magnitude in `amax`) is encoded
 // exactly like the allreduce's own encoder does - scale amax/448, e4m3 codes of
 // x / scale - and stored into every rank's staging slot for flattened element
 // `elem` of the [M,N] result.
-__device__ __forceinline__ void push_block128(const rdb::ar::PushTarget& t, const uint32_t* packed, float amax, size_t elem) {
+__device__ __forceinline__ void push_block128(const rdb::ar::PushTarget& t, const unsigned call, const uint32_t* packed, float amax, size_t elem) {
     const float s = rdb::ar::block_scale(amax);
     rdb::ar::BlockDivisor d;
     d.set(s);
     const size_t g = elem / 512;
     const int blk = static_cast<int>((elem % 512) / 128);
-    const size_t slot = (static_cast<size_t>(t.epoch & 1u) * t.world + t.rank) * t.slot_groups + g;
+    const size_t slot = (static_cast<size_t>(call & 1u) * t.world + t.rank) * t.slot_groups + g;
 #pragma unroll 1
     for (int i = 0; i < 8; i++) {                       // 16 elements -> 16 code bytes per step
         uint32_t q[4];
@@ -295,6 +302,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
         // preceding kernel until it has completed
         if (p.pdl) pdl_wait_prior();
         const unsigned epoch = ld_acquire_gpu_u32(p.words);
+        const unsigned push_call = push_call_number(p.push);
         float* my_slot = p.partial + static_cast<size_t>(cta) * SLOT_FLOATS + lane * MAX_R;
         int pi = 0, seg = 0;
         bool live = true;
@@ -385,7 +393,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
                                 amax = fmaxf(amax, fmaxf(fabsf(__uint_as_float(w << 16)), fabsf(__uint_as_float(w & 0xFFFF0000u))));
                             }
                         }
-                        if (lane < pr.M) push_block128(p.push, packed, amax, static_cast<size_t>(lane) * pr.N + n0 + b0);
+                        if (lane < pr.M) push_block128(p.push, push_call, packed, amax, static_cast<size_t>(lane) * pr.N + n0 + b0);
                     }
                 } else {
                     for (int c0 = 32 * e; c0 < pr.R; c0 += 64) {
@@ -426,9 +434,10 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
                 // every CTA has delivered and fenced: tell all ranks that this rank's blocks of the call are in
                 // place (the allreduce's "pushed" flag of this epoch; a wait that ran out here marks it failed)
                 __threadfence_system();
-                const unsigned word = (p.push.epoch << 1) | (atomicExch(p.words + 2, 0u) & 1u);
+                const unsigned call = push_call_number(p.push);
+                const unsigned word = (call << 1) | (atomicExch(p.words + 2, 0u) & 1u);
                 for (int k = 0; k < p.push.world; k++) {
-                    unsigned* f = reinterpret_cast<unsigned*>(p.push.ws[k] + p.push.off_flags) + (p.push.epoch & 1u) * 8 + p.push.rank;
+                    unsigned* f = reinterpret_cast<unsigned*>(p.push.ws[k] + p.push.off_flags) + (call & 1u) * 8 + p.push.rank;
                     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(f), "r"(word) : "memory");
                 }
             }

@@ -84,6 +84,55 @@ def main():
             dist.barrier()
     dist.barrier()
     ar.close()
+    # calls counted on the device, recorded in a CUDA graph and replayed with new inputs (three calls per replay, so the
+    # staging sets alternate between replays), then a direct call on the same object
+    cap = R.Fp8AllReduce(max_elems=1024 * 8192, backend="ipc", capturable=True)
+    sizes = (16 * 8192, 1024 * 8192, 513 * 1024 + 128)
+    xd = [torch.zeros(n, dtype=torch.bfloat16, device=dev) for n in sizes]
+    od = [torch.empty(n, dtype=torch.bfloat16, device=dev) for n in sizes]
+    algos = (1, 2, 3)
+
+    def inputs(rep):
+        return [[torch.randn(n, generator=torch.Generator().manual_seed(31 * rep + 7 * r + n)).bfloat16() * (rep + 1)
+                 for r in range(world)] for n in sizes]
+
+    def check_outputs(xs, what):
+        torch.cuda.synchronize()
+        assert R.lib().rdb_device_status() == 0, "device-side wait timed out"
+        for i, algo in enumerate(algos):
+            bits = np.stack([x.view(torch.int16).numpy().view(np.uint16) for x in xs[i]])
+            want = O.allreduce_fp8_regather(bits) if algo == 3 else O.allreduce_fp8(bits)[0]
+            got = od[i].cpu().view(torch.int16).numpy().view(np.uint16)
+            assert np.array_equal(got, want), f"rank {rank} {what} size {sizes[i]} algo {algo}: {(got != want).sum()} differ"
+        dist.barrier()
+
+    xs = inputs(0)
+    for i, algo in enumerate(algos):
+        xd[i].copy_(xs[i][rank])
+        cap.all_reduce(xd[i], out=od[i], algo=algo)          # before the capture: per-device set-up
+    check_outputs(xs, "direct")
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            for i, algo in enumerate(algos):
+                cap.all_reduce(xd[i], out=od[i], algo=algo)
+    torch.cuda.current_stream().wait_stream(side)
+    for rep in range(1, 5):
+        xs = inputs(rep)
+        for i in range(len(sizes)):
+            xd[i].copy_(xs[i][rank])
+            od[i].zero_()
+        graph.replay()
+        check_outputs(xs, f"replay {rep}")
+    xs = inputs(9)
+    for i, algo in enumerate(algos):
+        xd[i].copy_(xs[i][rank])
+        cap.all_reduce(xd[i], out=od[i], algo=algo)
+    check_outputs(xs, "direct after replays")
+    del graph
+    cap.close()
     dist.destroy_process_group()
     print(f"rank {rank} ok")
 

@@ -327,6 +327,76 @@ def test_fused_call_on_one_rank_and_its_trace(cuda_device, oracle):
 
 
 @pytest.mark.gpu
+def test_calls_recorded_in_a_cuda_graph(cuda_device, oracle):
+    """A context that counts its calls on the device: three allreduce calls (one-shot, two-shot, second variant) and a
+    GEMM + allreduce are recorded once and replayed with new inputs in the recorded buffers; every replay - an odd
+    number of calls each, so the staging sets alternate between replays - equals the oracle bit for bit, direct calls
+    in between included.  World size 1 here; the multi-rank form runs in the multi-GPU tests."""
+    import rocm_dev_b200 as R
+    from rocm_dev_b200 import quant
+    from rocm_dev_b200.allreduce import _Workspace, _create
+    from rocm_dev_b200.skinny_gemm import _problem_array
+    from rocm_dev_b200._lib import check
+    L = R.lib()
+    n, (M, N, K) = 128 * 1031, (8, 1024, 2048)
+    with torch.cuda.device(cuda_device):
+        ws = _Workspace(1, n)
+        ctx = _create(0, 1, [ws.ptr], n)
+        check(L.rdb_ar_set_device_epoch(ctx, 1), "rdb_ar_set_device_epoch")
+        assert L.rdb_ar_begin_call(ctx) == -1                                   # the separate phases need the host's count
+        xd = torch.zeros(n, dtype=torch.bfloat16, device=cuda_device)
+        outs = [torch.empty(n, dtype=torch.bfloat16, device=cuda_device) for _ in range(3)]
+        Aq, Bq, sa, sb = quant.synthetic_gemm_operands(M, N, K, seed=3)
+        A, B, dsa, dsb = Aq.to(cuda_device), Bq.to(cuda_device), sa.to(cuda_device), sb.to(cuda_device)
+        D = torch.empty((M, N), dtype=torch.bfloat16, device=cuda_device)
+        lin = torch.empty((M, N), dtype=torch.bfloat16, device=cuda_device)
+        assert R.skinny_gemm_fp8_grouped([(A, B, dsa, dsb, D)]) == 0
+        torch.cuda.synchronize()
+        want_lin = oracle.allreduce_fp8(_bits(D.reshape(-1))[None])[0]
+        arr = _problem_array([(A, B, dsa, dsb, lin)])
+
+        def issue(stream):
+            for algo, o in zip((1, 2, 3), outs):
+                check(L.rdb_ar_allreduce(ctx, xd.data_ptr(), o.data_ptr(), n, algo, stream), "rdb_ar_allreduce")
+            check(L.rdb_skinny_gemm_fp8_allreduce(ctx, arr, lin.data_ptr(), stream), "rdb_skinny_gemm_fp8_allreduce")
+
+        def verify(x):
+            torch.cuda.synchronize()
+            assert L.rdb_device_status() == 0
+            v1 = oracle.allreduce_fp8(_bits(x)[None])[0]
+            assert np.array_equal(_bits(outs[0]), v1) and np.array_equal(_bits(outs[1]), v1)
+            assert np.array_equal(_bits(outs[2]), oracle.allreduce_fp8_regather(_bits(x)[None]))
+            assert np.array_equal(_bits(lin.reshape(-1)), want_lin)
+
+        x = torch.randn(n, generator=torch.Generator().manual_seed(1)).bfloat16()
+        xd.copy_(x)
+        issue(torch.cuda.current_stream().cuda_stream)                           # before any capture: per-device set-up
+        verify(x)
+        assert L.rdb_ar_set_device_epoch(ctx, 0) == 6                            # too late to change the way of counting
+        graph = torch.cuda.CUDAGraph()
+        side = torch.cuda.Stream(device=cuda_device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                issue(side.cuda_stream)
+        torch.cuda.current_stream().wait_stream(side)
+        for rep in range(5):
+            x = torch.randn(n, generator=torch.Generator().manual_seed(10 + rep)).bfloat16() * (rep + 1)
+            xd.copy_(x)
+            for o in outs:
+                o.zero_()
+            lin.zero_()
+            graph.replay()
+            verify(x)
+            if rep == 2:                                                          # a direct call between two replays
+                check(L.rdb_ar_allreduce(ctx, xd.data_ptr(), outs[0].data_ptr(), n, 2, torch.cuda.current_stream().cuda_stream), "direct")
+                verify(x)
+        del graph
+        L.rdb_ar_destroy(ctx)
+        ws.free()
+
+
+@pytest.mark.gpu
 def test_error_codes(cuda_device):
     import ctypes as C
     import rocm_dev_b200 as R
