@@ -239,6 +239,14 @@ int rdb_sparse_gemm_fp8(const uint8_t *A, const uint8_t *Wvals, const uint8_t *W
 /* Same with the K split (1, 2 or 4 CTAs per cluster; 0 = automatic) chosen by the caller. */
 int rdb_sparse_gemm_fp8_tuned(const uint8_t *A, const uint8_t *Wvals, const uint8_t *Wmeta, const float *scale_a,
                               const float *scale_b, uint16_t *D, int M, int N, int K, int split_k, void *stream);
+/* Same with launch flags: RDB_SKINNY_OVERLAP_PRIOR_KERNEL lets the kernel start
+ * while the preceding kernel of the stream drains - it requests its first
+ * ring-full of compressed weights and metadata at once and waits for that
+ * kernel only before it reads A, the scales or writes D; the preceding kernel
+ * must not write Wvals or Wmeta (a decode loop). */
+int rdb_sparse_gemm_fp8_flags(const uint8_t *A, const uint8_t *Wvals, const uint8_t *Wmeta, const float *scale_a,
+                              const float *scale_b, uint16_t *D, int M, int N, int K, int split_k, unsigned flags,
+                              void *stream);
 /* Host-side packer (no GPU): Wq [N,K] e4m3 bytes that already are 2:4 ->
  * vals [N,K/2] and meta.  Returns RDB_INVALID_CONFIG if a group of four holds
  * more than two non-zero bytes.  rdb_sparse_meta_bytes gives meta's size (0 for

@@ -61,6 +61,7 @@ struct Params {
     int NB;                    // padded batch columns per CTA (UMMA N); blockIdx.z selects the batch block
     int nstages;
     int ring_bytes;
+    int pdl;                   // launched with programmatic stream serialization
 };
 
 // e4m3 x e4m3 -> f32, K-major operands, sparse A.
@@ -139,13 +140,31 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     if (S > 1) cluster_arrive_release();              // phase 1: "my barriers and buffers are live"
+    if (p.pdl) pdl_launch_dependents();               // the next kernel in the stream may start its prologue
 
     if (warp == 0) {
         if (lane == 0) {
             // with several batch blocks the weights are read once per block: keep them in L2 for the sibling
             const uint64_t pol_w = gridDim.z > 1 ? l2_policy_evict_last() : l2_policy_evict_first(), pol_x = l2_policy_evict_last();
             const uint8_t* meta_tile = p.meta + static_cast<size_t>(tile) * (2 * p.num_kb) * ATOM_BYTES;
-            for (int i = 0; i < nkb; i++) {
+            // The compressed weights and their metadata never depend on the preceding kernel: the first ring-full is
+            // requested before waiting for that kernel to finish; the activations may be its output.
+            const int pre = nkb < nstages ? nkb : nstages;
+            for (int i = 0; i < pre; i++) {
+                const int kb = kb_begin + i;
+                const uint32_t dst = stage0 + i * STAGE, bar = full0 + 8 * i;
+                mbar_arrive_expect_tx(bar, STAGE);
+                tma_load_2d(dst, &tmW, kb * BKC, n0, bar, pol_w);
+                bulk_load(dst + A_BYTES + 2 * NB * 128, meta_tile + static_cast<size_t>(2 * kb) * ATOM_BYTES, E_BYTES, bar);
+            }
+            if (p.pdl) pdl_wait_prior();
+            for (int i = 0; i < pre; i++) {
+                const int kb = kb_begin + i;
+                const uint32_t dst = stage0 + i * STAGE, bar = full0 + 8 * i;
+                tma_load_2d(dst + A_BYTES, &tmX, kb * 256, m0, bar, pol_x);
+                tma_load_2d(dst + A_BYTES + NB * 128, &tmX, kb * 256 + 128, m0, bar, pol_x);
+            }
+            for (int i = pre; i < nkb; i++) {
                 const int s = i % nstages;
                 const uint32_t ph = (i / nstages) & 1;
                 if (!mbar_wait(empty0 + 8 * s, ph ^ 1)) { *abort_flag = 1; report_timeout(p.status); break; }
@@ -206,6 +225,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
     if (S > 1) cluster_wait_acquire();
     __syncthreads();
+    if (p.pdl) pdl_wait_prior();                       // D and the scales may belong to the preceding kernel
     const float sc = __ldg(p.scale_a) * __ldg(p.scale_b);
 
     if (S == 1) {
@@ -261,7 +281,8 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 }
 
 static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* sa, const float* sb, uint16_t* D,
-               int M, int N, int K, int split_k_hint, cudaStream_t stream) {
+               int M, int N, int K, int split_k_hint, unsigned flags, cudaStream_t stream) {
+    if (flags & ~RDB_SKINNY_OVERLAP_PRIOR_KERNEL) return RDB_INVALID_CONFIG;
     if (M < 1 || N < 1 || K < 1) return RDB_BAD_SHAPE;
     if (M > 256) return RDB_M_ABOVE_WARPTILE_M;
     if (N % 2 != 0) return RDB_N_NOT_EVEN;
@@ -322,19 +343,23 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
     int ring = stages * stage_bytes(NB);
     if (ring < stg_bytes(NB)) ring = stg_bytes(NB);
     p.ring_bytes = ring;
+    const bool pdl = (flags & RDB_SKINNY_OVERLAP_PRIOR_KERNEL) != 0;
+    p.pdl = pdl ? 1 : 0;
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(S, tiles, mblocks);
     cfg.blockDim = dim3(NUM_THREADS, 1, 1);
     cfg.dynamicSmemBytes = smem_bytes(NB, S, stages);
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = S;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pdl ? 2 : 1;
     return cudaLaunchKernelEx(&cfg, sparse_gemm_kernel, tmW, tmX, p) == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
 }
 
@@ -386,12 +411,17 @@ int rdb_sparse_pack_2of4(const uint8_t* Wq, int N, int K, uint8_t* vals, uint8_t
 
 int rdb_sparse_gemm_fp8(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* scale_a,
                         const float* scale_b, uint16_t* D, int M, int N, int K, void* stream) {
-    return rdb::sparse::run(A, Wvals, Wmeta, scale_a, scale_b, D, M, N, K, 0, static_cast<cudaStream_t>(stream));
+    return rdb::sparse::run(A, Wvals, Wmeta, scale_a, scale_b, D, M, N, K, 0, 0, static_cast<cudaStream_t>(stream));
 }
 
 int rdb_sparse_gemm_fp8_tuned(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* scale_a,
                               const float* scale_b, uint16_t* D, int M, int N, int K, int split_k, void* stream) {
-    return rdb::sparse::run(A, Wvals, Wmeta, scale_a, scale_b, D, M, N, K, split_k, static_cast<cudaStream_t>(stream));
+    return rdb::sparse::run(A, Wvals, Wmeta, scale_a, scale_b, D, M, N, K, split_k, 0, static_cast<cudaStream_t>(stream));
+}
+
+int rdb_sparse_gemm_fp8_flags(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* scale_a,
+                              const float* scale_b, uint16_t* D, int M, int N, int K, int split_k, unsigned flags, void* stream) {
+    return rdb::sparse::run(A, Wvals, Wmeta, scale_a, scale_b, D, M, N, K, split_k, flags, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

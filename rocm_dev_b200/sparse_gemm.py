@@ -69,8 +69,11 @@ def load_2of4(path: str):
 
 
 def sparse_gemm_fp8(A: torch.Tensor, vals: torch.Tensor, meta: torch.Tensor, scale_a: torch.Tensor,
-                    scale_b: torch.Tensor, out: torch.Tensor | None = None, split_k: int = 0) -> torch.Tensor:
-    """D[M,N] = bf16((A . W^T) * scale_a * scale_b) with W given compressed."""
+                    scale_b: torch.Tensor, out: torch.Tensor | None = None, split_k: int = 0, flags: int = 0) -> torch.Tensor:
+    """D[M,N] = bf16((A . W^T) * scale_a * scale_b) with W given compressed.
+    ``flags``: 0 or ``OVERLAP_PRIOR_KERNEL`` (1): the launch may start streaming
+    weights while the preceding kernel of the stream drains (that kernel must not
+    write the weights)."""
     assert A.is_cuda and vals.is_cuda and meta.is_cuda and A.is_contiguous() and vals.is_contiguous()
     A = A if A.dtype == torch.uint8 else A.view(torch.uint8)
     M, K = A.shape
@@ -79,7 +82,7 @@ def sparse_gemm_fp8(A: torch.Tensor, vals: torch.Tensor, meta: torch.Tensor, sca
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=A.device)
     with torch.cuda.device(A.device):
-        check(lib().rdb_sparse_gemm_fp8_tuned(A.data_ptr(), vals.data_ptr(), meta.data_ptr(), scale_a.data_ptr(),
-                                              scale_b.data_ptr(), out.data_ptr(), M, N, K, split_k,
+        check(lib().rdb_sparse_gemm_fp8_flags(A.data_ptr(), vals.data_ptr(), meta.data_ptr(), scale_a.data_ptr(),
+                                              scale_b.data_ptr(), out.data_ptr(), M, N, K, split_k, flags,
                                               torch.cuda.current_stream(A.device).cuda_stream), "rdb_sparse_gemm_fp8")
     return out

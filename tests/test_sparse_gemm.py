@@ -184,6 +184,39 @@ def test_config3_matches_oracle_and_own_dense_kernel(cuda_device, oracle, M):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K,split_k", [(16, 1024, 4096, 0), (64, 512, 2048, 2), (200, 384, 1024, 1)])
+def test_launches_that_overlap_their_predecessor(cuda_device, oracle, M, N, K, split_k):
+    """OVERLAP_PRIOR_KERNEL: a chain of launches in which each one's activations are the previous one's business
+    (here: a kernel that rewrites A between the GEMMs) gives the bits of ordinary launches."""
+    import rocm_dev_b200 as R
+    from rocm_dev_b200 import quant
+    dev = cuda_device
+    Wq, sb = _sparse_weights(N, K, 3)
+    vals, meta = R.pack_2of4(Wq)
+    vals, meta, dsb = vals.to(dev), meta.to(dev), sb.to(dev)
+    acts = [quant.quantize_per_tensor(torch.randn((M, K), generator=torch.Generator().manual_seed(40 + i)).bfloat16()) for i in range(3)]
+    A = torch.empty((M, K), dtype=torch.uint8, device=dev)
+    sa = torch.empty(1, dtype=torch.float32, device=dev)
+    outs = {}
+    for flags in (0, R.OVERLAP_PRIOR_KERNEL):
+        res = []
+        for Aq, s in acts:
+            A.copy_(Aq.to(dev))                       # the preceding kernels of the stream write A and its scale
+            sa.copy_(s.to(dev))
+            res.append(R.sparse_gemm_fp8(A, vals, meta, sa, dsb, split_k=split_k, flags=flags).clone())
+        torch.cuda.synchronize()
+        assert R.lib().rdb_device_status() == 0
+        outs[flags] = res
+    for a, b in zip(outs[0], outs[R.OVERLAP_PRIOR_KERNEL]):
+        assert torch.equal(a, b)
+    ref = oracle.gemm_fp8_bf16(acts[2][0].numpy(), Wq.numpy(), acts[2][1].item(), sb.item())
+    ref64, mag = oracle.gemm_fp8_f64(acts[2][0].numpy(), Wq.numpy(), acts[2][1].item(), sb.item())
+    check_gemm_parity(bf16_bits(outs[R.OVERLAP_PRIOR_KERNEL][2]), ref, ref64, mag, K)
+    with pytest.raises(Exception):
+        R.sparse_gemm_fp8(A, vals, meta, sa, dsb, flags=2)
+
+
+@pytest.mark.gpu
 def test_error_codes(cuda_device):
     import rocm_dev_b200 as R
     L = R.lib()
