@@ -39,7 +39,8 @@ constexpr int NUM_THREADS = 192;
 constexpr int MAX_STAGES = 8;
 constexpr int BAR_BYTES = 256;
 constexpr int SMEM_LIMIT = 232448;
-constexpr int TMEM_E_COL = 256;         // metadata columns start here: 8 per stage
+// TMEM: accumulator columns [0, NB), then 8 metadata columns per stage from column max(NB, 32) on; the allocation is
+// the next power of two, so a narrow batch leaves TMEM (and, with a short ring, shared memory) for a second CTA on the SM
 
 __host__ __device__ constexpr int stage_bytes(int NB) { return A_BYTES + 2 * NB * 128 + E_BYTES; }
 __host__ __device__ constexpr int red_bytes(int NB, int S) { return S > 1 ? BM * NB * 4 : 0; }   // [S][128/S rows][NB]
@@ -62,6 +63,7 @@ struct Params {
     int nstages;
     int ring_bytes;
     int pdl;                   // launched with programmatic stream serialization
+    int te_col, tmem_cols;     // first metadata column, allocated columns (power of two)
 };
 
 // e4m3 x e4m3 -> f32, K-major operands, sparse A.
@@ -132,7 +134,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (S > 1) mbar_arrive_expect_tx(xbar, static_cast<uint32_t>(S) * rows_per * NB * 4u);
     }
     if (warp == 1) {
-        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_alloc(smem_u32(tmem_slot), p.tmem_cols);
         tmem_relinquish();
     }
     tc_fence_before_sync();
@@ -187,7 +189,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                 if (!mbar_wait(full0 + 8 * s, ph)) { *abort_flag = 1; report_timeout(p.status); break; }
                 tc_fence_after_sync();
                 const uint32_t a = stage0 + s * STAGE, b = a + A_BYTES, e = b + 2 * NB * 128;
-                const uint32_t te = tmem_base + TMEM_E_COL + 8 * s;
+                const uint32_t te = tmem_base + p.te_col + 8 * s;
                 tmem_cp_128x128b(te, smem_desc_meta(e));
                 tmem_cp_128x128b(te + 4, smem_desc_meta(e + ATOM_BYTES));
 #pragma unroll
@@ -277,7 +279,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     }
     tc_fence_before_sync();
     __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem_base, 512);
+    if (warp == 1) tmem_dealloc(tmem_base, p.tmem_cols);
 }
 
 static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* sa, const float* sb, uint16_t* D,
@@ -308,7 +310,12 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
         }
     }
     while (S > 1 && (S > num_kb || NB > 64)) S /= 2;
-    int stages = (200 * 1024 - red_bytes(NB, S)) / stage_bytes(NB);
+    const bool pdl = (flags & RDB_SKINNY_OVERLAP_PRIOR_KERNEL) != 0;
+    // A launch that may overlap its predecessor keeps its ring to under half of an SM's shared memory (and, below,
+    // its TMEM to half of the columns) when the batch is narrow: its CTAs can then become resident beside the
+    // predecessor's and stream their first weights while those are still in their epilogue.
+    const int ring_budget = (pdl && NB <= 32) ? 108 * 1024 : 200 * 1024;   // wider batches: too few stages (measured slower)
+    int stages = (ring_budget - red_bytes(NB, S)) / stage_bytes(NB);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     const int kb_per = (num_kb + S - 1) / S;
     if (stages > kb_per) stages = kb_per;
@@ -322,6 +329,8 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
     if (!attr_set[dev]) {
         if (cudaFuncSetAttribute(sparse_gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_LIMIT) != cudaSuccess)
             return RDB_CUDA_ERROR;
+        // two half-ring CTAs of consecutive launches share an SM only if the SM is carved for shared memory
+        cudaFuncSetAttribute(sparse_gemm_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         attr_set[dev] = true;
     }
     CUtensorMap tmW, tmX;
@@ -343,8 +352,10 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
     int ring = stages * stage_bytes(NB);
     if (ring < stg_bytes(NB)) ring = stg_bytes(NB);
     p.ring_bytes = ring;
-    const bool pdl = (flags & RDB_SKINNY_OVERLAP_PRIOR_KERNEL) != 0;
     p.pdl = pdl ? 1 : 0;
+    p.te_col = NB < 32 ? 32 : NB;
+    p.tmem_cols = 32;
+    while (p.tmem_cols < p.te_col + 8 * stages) p.tmem_cols *= 2;
 
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(S, tiles, mblocks);
