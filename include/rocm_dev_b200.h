@@ -251,6 +251,12 @@ int rdb_sparse_gemm_fp8_flags(const uint8_t *A, const uint8_t *Wvals, const uint
  * vals [N,K/2] and meta.  Returns RDB_INVALID_CONFIG if a group of four holds
  * more than two non-zero bytes.  rdb_sparse_meta_bytes gives meta's size (0 for
  * an unsupported shape). */
+/* Diagnostics: registers a device buffer of slots x 8 uint64.  While registered,
+ * sparse launch i writes %globaltimer stamps of its first CTA (entry, set-up
+ * done, first stage full, last stage's MMAs issued, accumulator complete,
+ * partials exchanged, stores issued, exit) into slot i % slots.  NULL switches
+ * it off.  Not thread-safe; leave off in production. */
+int rdb_sparse_gemm_trace(unsigned long long *device_buffer, int slots);
 size_t rdb_sparse_meta_bytes(int N, int K);
 int rdb_sparse_pack_2of4(const uint8_t *Wq, int N, int K, uint8_t *vals, uint8_t *meta);
 

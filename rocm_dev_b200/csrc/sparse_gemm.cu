@@ -64,7 +64,13 @@ struct Params {
     int ring_bytes;
     int pdl;                   // launched with programmatic stream serialization
     int te_col, tmem_cols;     // first metadata column, allocated columns (power of two)
+    unsigned long long* trace; // optional: 8 %globaltimer stamps of the launch's first CTA (diagnostics), else nullptr
 };
+
+// entry, set-up done, first stage full, last stage's MMAs issued, accumulator complete, partials exchanged, stores issued, exit
+__device__ __forceinline__ void stamp(const Params& p, int slot) {
+    if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) p.trace[slot] = globaltimer_ns();
+}
 
 // e4m3 x e4m3 -> f32, K-major operands, sparse A.
 __host__ __device__ constexpr uint32_t idesc_sparse(int umma_m, int umma_n) {
@@ -102,6 +108,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = gridDim.x, rank = blockIdx.x;      // cluster = K slices of one tile
+    if (threadIdx.x == 0) stamp(p, 0);
     const int tile = blockIdx.y, n0 = tile * BM;
     const int m0 = blockIdx.z * p.NB;                 // first batch row of this CTA
     const int m_count = p.M - m0 < p.NB ? p.M - m0 : p.NB;
@@ -141,6 +148,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    if (threadIdx.x == 0) stamp(p, 1);
     if (S > 1) cluster_arrive_release();              // phase 1: "my barriers and buffers are live"
     if (p.pdl) pdl_launch_dependents();               // the next kernel in the stream may start its prologue
 
@@ -188,6 +196,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                 const uint32_t ph = (i / nstages) & 1;
                 if (!mbar_wait(full0 + 8 * s, ph)) { *abort_flag = 1; report_timeout(p.status); break; }
                 tc_fence_after_sync();
+                if (i == 0) stamp(p, 2);
                 const uint32_t a = stage0 + s * STAGE, b = a + A_BYTES, e = b + 2 * NB * 128;
                 const uint32_t te = tmem_base + p.te_col + 8 * s;
                 tmem_cp_128x128b(te, smem_desc_meta(e));
@@ -199,6 +208,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                 tc_commit(empty0 + 8 * s);
             }
             tc_commit(tmem_full);
+            stamp(p, 3);
         }
         __syncwarp();
     }
@@ -212,6 +222,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (!ok) { *abort_flag = 1; report_timeout(p.status); }
         ok = ok && (*abort_flag == 0);
         tc_fence_after_sync();
+        if (warp == 2 && lane == 0) stamp(p, 4);
         if (ok) {
             const int quad = warp & 3;
             float* row = stg + (quad * 32 + lane) * pitch;
@@ -256,6 +267,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
         if (!mbar_wait(xbar, 0)) { *abort_flag = 1; report_timeout(p.status); }
         __syncthreads();
+        if (threadIdx.x == 0) stamp(p, 5);
         if (*abort_flag == 0) {
             for (int item = threadIdx.x; item < m_count * (rows_per / 2); item += NUM_THREADS) {
                 const int m = item / (rows_per / 2), rl = (item - m * (rows_per / 2)) * 2;
@@ -274,13 +286,18 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         }
     }
 
+    if (threadIdx.x == 0) stamp(p, 6);
     if (*abort_flag != 0) {
         for (int i = 0; i < 64; i++) __nanosleep(2000);
     }
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, p.tmem_cols);
+    if (threadIdx.x == 0) stamp(p, 7);
 }
+
+static unsigned long long* g_trace = nullptr;
+static int g_trace_slots = 0, g_trace_next = 0;
 
 static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* sa, const float* sb, uint16_t* D,
                int M, int N, int K, int split_k_hint, unsigned flags, cudaStream_t stream) {
@@ -353,6 +370,7 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
     if (ring < stg_bytes(NB)) ring = stg_bytes(NB);
     p.ring_bytes = ring;
     p.pdl = pdl ? 1 : 0;
+    p.trace = g_trace ? g_trace + static_cast<size_t>(g_trace_next++ % g_trace_slots) * 8 : nullptr;
     p.te_col = NB < 32 ? 32 : NB;
     p.tmem_cols = 32;
     while (p.tmem_cols < p.te_col + 8 * stages) p.tmem_cols *= 2;
@@ -428,6 +446,14 @@ int rdb_sparse_gemm_fp8(const uint8_t* A, const uint8_t* Wvals, const uint8_t* W
 int rdb_sparse_gemm_fp8_tuned(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* scale_a,
                               const float* scale_b, uint16_t* D, int M, int N, int K, int split_k, void* stream) {
     return rdb::sparse::run(A, Wvals, Wmeta, scale_a, scale_b, D, M, N, K, split_k, 0, static_cast<cudaStream_t>(stream));
+}
+
+int rdb_sparse_gemm_trace(unsigned long long* device_buffer, int slots) {
+    if (device_buffer && slots < 1) return RDB_INVALID_CONFIG;
+    rdb::sparse::g_trace = device_buffer;
+    rdb::sparse::g_trace_slots = slots;
+    rdb::sparse::g_trace_next = 0;
+    return RDB_SUCCESS;
 }
 
 int rdb_sparse_gemm_fp8_flags(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* scale_a,
