@@ -314,6 +314,8 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
             const int seg_end = tile_end < hi ? tile_end : hi;
             const bool from_k0 = kb0 == 0, to_k_end = seg_end == tile_end;
             const int buf = seg & 1;
+            // fetched now, used after the accumulator wait: the load latency hides behind the segment's MMAs
+            const float sc = from_k0 ? __ldg(pr.scale_a) * __ldg(pr.scale_b) : 0.0f;
             // A tile whose head I hold (always my last segment) is mine to finish.  Its other parts were computed by
             // the following CTAs at the START of their ranges, so their flags are normally up long before my last MMA:
             // find them and poll them now, one lane per flag (each poll is an L2 round trip), while the MMAs run.
@@ -358,7 +360,6 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
                     st_release_gpu_u32(p.words + 8 + 2 * cta + e, epoch + 1);
                 }
             } else {
-                const float sc = __ldg(pr.scale_a) * __ldg(pr.scale_b);
                 // the partners' parts of 32 columns of my row, added in K order; the loads of a part are issued
                 // together (eight independent 16-byte loads per lane)
                 auto add_parts = [&](int c0, float* v) {

@@ -43,8 +43,8 @@ constexpr int SMEM_LIMIT = 232448;
 // the next power of two, so a narrow batch leaves TMEM (and, with a short ring, shared memory) for a second CTA on the SM
 
 __host__ __device__ constexpr int stage_bytes(int NB) { return A_BYTES + 2 * NB * 128 + E_BYTES; }
-__host__ __device__ constexpr int red_bytes(int NB, int S) { return S > 1 ? BM * NB * 4 : 0; }   // [S][128/S rows][NB]
-__host__ __device__ constexpr int stg_bytes(int NB) { return BM * (NB + 4) * 4; }
+__host__ __device__ constexpr int red_bytes(int NB, int S) { return S > 1 ? BM * NB * 4 : 0; }   // [S][NB][128/S rows]
+__host__ __device__ constexpr int stg_bytes(int NB) { return NB * (BM + 4) * 4; }   // [NB][128 + 4]: one line per batch row
 __host__ __device__ inline int smem_bytes(int NB, int S, int stages) {
     int ring = stages * stage_bytes(NB);
     if (ring < stg_bytes(NB)) ring = stg_bytes(NB);     // the staging tile reuses the drained ring
@@ -124,6 +124,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     const uint32_t tmem_full = smem_u32(bars + 2 * MAX_STAGES), xbar = smem_u32(bars + 2 * MAX_STAGES + 1);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * MAX_STAGES + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* sc_slot = reinterpret_cast<float*>(tmem_slot + 2);
     const uint32_t stage0 = smem_u32(smem);
     const int rows_per = BM / S;                      // S is 1, 2 or 4
 
@@ -213,11 +214,19 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         __syncwarp();
     }
 
-    // ---- epilogue: warps 2..5 move their TMEM lane quadrant (32 weight rows
-    // each) into the staging tile stg[row][NB] (pitch NB+4) in the drained ring.
+    // ---- epilogue: warps 2..5 move their TMEM lane quadrant (32 weight rows each) into the staging tile in the
+    // drained ring.  The tile is kept TRANSPOSED - stg[batch row m][weight row r], lines of 128 + 4 floats - because D
+    // is written along n: the threads of a warp then read consecutive floats (no bank conflicts; with stg[r][m] a warp
+    // that writes 128 contiguous output bytes reads 32 floats that all lie in one bank) and write whole 128-byte lines.
     float* stg = reinterpret_cast<float*>(smem);
-    const int pitch = NB + 4;
+    constexpr int pitch = BM + 4;
     if (warp >= 2) {
+        // the two scales are fetched while the weights stream: their global-load latency (about a microsecond
+        // when they miss L2) would otherwise sit between the last MMA and the first store
+        if (warp == 2 && lane == 0) {
+            if (p.pdl) pdl_wait_prior();               // the scales may be the preceding kernel's output
+            *sc_slot = __ldg(p.scale_a) * __ldg(p.scale_b);
+        }
         bool ok = mbar_wait(tmem_full, 0);
         if (!ok) { *abort_flag = 1; report_timeout(p.status); }
         ok = ok && (*abort_flag == 0);
@@ -225,63 +234,69 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         if (warp == 2 && lane == 0) stamp(p, 4);
         if (ok) {
             const int quad = warp & 3;
-            float* row = stg + (quad * 32 + lane) * pitch;
+            float* col = stg + quad * 32 + lane;           // this thread's weight row
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16);
 #pragma unroll 1
             for (int c0 = 0; c0 < NB; c0 += 16) {
                 float v[16];
                 tmem_ld16(taddr + c0, v);
 #pragma unroll
-                for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(row + c0 + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                for (int j = 0; j < 16; j++) col[(c0 + j) * pitch] = v[j];
             }
         }
     }
     if (S > 1) cluster_wait_acquire();
     __syncthreads();
-    if (p.pdl) pdl_wait_prior();                       // D and the scales may belong to the preceding kernel
-    const float sc = __ldg(p.scale_a) * __ldg(p.scale_b);
+    if (p.pdl) pdl_wait_prior();                       // D may still be read by the preceding kernel's successors
+    const float sc = *sc_slot;
 
+    // one bf16x2 store per item (batch row m, pair of weight rows); consecutive threads take consecutive pairs
+    auto store_pair = [&](int m, int n, float v0, float v1) {
+        if (n + 1 < p.N) {
+            *reinterpret_cast<__nv_bfloat162*>(p.D + static_cast<size_t>(m0 + m) * p.N + n) = __floats2bfloat162_rn(v0 * sc, v1 * sc);
+        } else if (n < p.N) {
+            p.D[static_cast<size_t>(m0 + m) * p.N + n] = __float2bfloat16_rn(v0 * sc);
+        }
+    };
     if (S == 1) {
         if (*abort_flag == 0) {
-            // item = (batch row m, pair of weight rows): one bf16x2 store, coalesced along n
+            // six warps cannot hide the latency chain of one item per thread: four independent items per trip
+#pragma unroll 4
             for (int item = threadIdx.x; item < m_count * (BM / 2); item += NUM_THREADS) {
                 const int m = item / (BM / 2), r = (item - m * (BM / 2)) * 2;
-                const int n = n0 + r;
-                if (n + 1 < p.N) {
-                    *reinterpret_cast<__nv_bfloat162*>(p.D + static_cast<size_t>(m0 + m) * p.N + n) =
-                        __floats2bfloat162_rn(stg[r * pitch + m] * sc, stg[(r + 1) * pitch + m] * sc);
-                } else if (n < p.N) {
-                    p.D[static_cast<size_t>(m0 + m) * p.N + n] = __float2bfloat16_rn(stg[r * pitch + m] * sc);
-                }
+                const float2 v = *reinterpret_cast<const float2*>(stg + m * pitch + r);
+                store_pair(m, n0 + r, v.x, v.y);
             }
         }
     } else {
-        // push: item = (weight row, 4-column granule) -> the rank that owns the row
-        const int G = NB / 4;
-        for (int item = threadIdx.x; item < BM * G; item += NUM_THREADS) {
-            const int r = item / G, g = item - r * G;
-            const int owner = r / rows_per, rl = r - owner * rows_per;
-            const float4 v = *reinterpret_cast<const float4*>(stg + r * pitch + 4 * g);
-            const uint32_t dst = mapa_smem(smem_u32(red + (static_cast<size_t>(rank) * rows_per + rl) * NB + 4 * g), owner);
+        // push: item = (batch row, granule of 4 weight rows) -> the rank that owns those rows; red[src][m][row] there
+        const int rows_shift = S == 2 ? 6 : 5;              // rows_per = 128 / S, S is 2 or 4 here
+#pragma unroll 4
+        for (int item = threadIdx.x; item < NB * (BM / 4); item += NUM_THREADS) {
+            const int m = item / (BM / 4), r = (item - m * (BM / 4)) * 4;
+            const int owner = r >> rows_shift, rl = r - (owner << rows_shift);
+            const float4 v = *reinterpret_cast<const float4*>(stg + m * pitch + r);
+            const uint32_t dst = mapa_smem(smem_u32(red + (static_cast<size_t>(rank) * NB + m) * rows_per + rl), owner);
             st_async_v4(dst, v.x, v.y, v.z, v.w, mapa_smem(xbar, owner));
         }
         if (!mbar_wait(xbar, 0)) { *abort_flag = 1; report_timeout(p.status); }
         __syncthreads();
         if (threadIdx.x == 0) stamp(p, 5);
         if (*abort_flag == 0) {
-            for (int item = threadIdx.x; item < m_count * (rows_per / 2); item += NUM_THREADS) {
-                const int m = item / (rows_per / 2), rl = (item - m * (rows_per / 2)) * 2;
+            const int pairs = rows_per / 2, pair_shift = rows_shift - 1;
+#pragma unroll 4
+            for (int item = threadIdx.x; item < m_count * pairs; item += NUM_THREADS) {
+                const int m = item >> pair_shift, rl = (item - (m << pair_shift)) * 2;
                 float s0 = 0.f, s1 = 0.f;
-                for (int src = 0; src < S; src++) {                 // rank order
-                    s0 += red[(static_cast<size_t>(src) * rows_per + rl) * NB + m];
-                    s1 += red[(static_cast<size_t>(src) * rows_per + rl + 1) * NB + m];
+#pragma unroll
+                for (int src = 0; src < 4; src++) {                 // rank order
+                    if (src < S) {
+                        const float2 v = *reinterpret_cast<const float2*>(red + ((src * NB + m) << rows_shift) + rl);
+                        s0 += v.x;
+                        s1 += v.y;
+                    }
                 }
-                const int n = n0 + rank * rows_per + rl;
-                if (n + 1 < p.N) {
-                    *reinterpret_cast<__nv_bfloat162*>(p.D + static_cast<size_t>(m0 + m) * p.N + n) = __floats2bfloat162_rn(s0 * sc, s1 * sc);
-                } else if (n < p.N) {
-                    p.D[static_cast<size_t>(m0 + m) * p.N + n] = __float2bfloat16_rn(s0 * sc);
-                }
+                store_pair(m, n0 + rank * rows_per + rl, s0, s1);
             }
         }
     }
