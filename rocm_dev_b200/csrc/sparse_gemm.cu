@@ -39,8 +39,8 @@ constexpr int NUM_THREADS = 192;
 constexpr int MAX_STAGES = 8;
 constexpr int BAR_BYTES = 256;
 constexpr int SMEM_LIMIT = 232448;
-// TMEM: accumulator columns [0, NB), then 8 metadata columns per stage from column max(NB, 32) on; the allocation is
-// the next power of two, so a narrow batch leaves TMEM (and, with a short ring, shared memory) for a second CTA on the SM
+// TMEM: two accumulators (even and odd k-blocks) of NB columns, a multiple of 32 apart, then 8 metadata columns per
+// stage; the allocation is the next power of two, so a narrow batch leaves TMEM (and, with a short ring, shared memory) for a second CTA on the SM
 
 __host__ __device__ constexpr int stage_bytes(int NB) { return A_BYTES + 2 * NB * 128 + E_BYTES; }
 __host__ __device__ constexpr int red_bytes(int NB, int S) { return S > 1 ? BM * NB * 4 : 0; }   // [S][NB][128/S rows]
@@ -64,6 +64,8 @@ struct Params {
     int ring_bytes;
     int pdl;                   // launched with programmatic stream serialization
     int te_col, tmem_cols;     // first metadata column, allocated columns (power of two)
+    int acc_stride;            // column distance between the accumulators
+    int issuers;               // MMA-issuing threads (2 or 4), each with its own accumulator and every issuers-th k-block
     unsigned long long* trace; // optional: 8 %globaltimer stamps of the launch's first CTA (diagnostics), else nullptr
 };
 
@@ -135,7 +137,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             mbar_init(full0 + 8 * s, 1);
             mbar_init(empty0 + 8 * s, 1);
         }
-        mbar_init(tmem_full, 1);
+        mbar_init(tmem_full, p.issuers);              // one commit from each issuing thread
         mbar_init(xbar, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -189,10 +191,22 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
+    } else if (warp >= 1 && warp <= p.issuers) {
+        // Several issuing threads: per stage one thread spends about half a microsecond on its barrier wait, fence, two
+        // metadata copies, four MMAs and the commit - 24 KiB per 0.5 us is less than an SM can draw from HBM - so
+        // lane 0 of warps 1 .. issuers (the later ones before they join the epilogue) each take every issuers-th
+        // k-block into an accumulator of their own; the epilogue adds the accumulators.
         if (lane == 0) {
+            const int which = warp - 1;
+            if (which == 1) {
+                // the two scales are fetched while the weights stream: their global-load latency (about a microsecond
+                // when they miss L2) would otherwise sit between the last MMA and the first store
+                if (p.pdl) pdl_wait_prior();               // the scales may be the preceding kernel's output
+                *sc_slot = __ldg(p.scale_a) * __ldg(p.scale_b);
+            }
             const uint32_t idesc = idesc_sparse(BM, NB);
-            for (int i = 0; i < nkb; i++) {
+            const uint32_t acc = tmem_base + which * p.acc_stride;
+            for (int i = which; i < nkb; i += p.issuers) {
                 const int s = i % nstages;
                 const uint32_t ph = (i / nstages) & 1;
                 if (!mbar_wait(full0 + 8 * s, ph)) { *abort_flag = 1; report_timeout(p.status); break; }
@@ -204,12 +218,12 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
                 tmem_cp_128x128b(te + 4, smem_desc_meta(e + ATOM_BYTES));
 #pragma unroll
                 for (int j = 0; j < 4; j++)
-                    tc_mma_sp_f8(tmem_base, smem_desc_k128(a + 32 * j), smem_desc_k128(b + (j >> 1) * NB * 128 + (j & 1) * 64),
-                                 te + 2 * j, idesc, (i | j) != 0);
+                    tc_mma_sp_f8(acc, smem_desc_k128(a + 32 * j), smem_desc_k128(b + (j >> 1) * NB * 128 + (j & 1) * 64),
+                                 te + 2 * j, idesc, (i >= p.issuers) || j != 0);
                 tc_commit(empty0 + 8 * s);
             }
-            tc_commit(tmem_full);
-            stamp(p, 3);
+            tc_commit(tmem_full);                          // (also after an abort, and from a thread that had no k-block)
+            if (which == 0) stamp(p, 3);
         }
         __syncwarp();
     }
@@ -221,12 +235,6 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
     float* stg = reinterpret_cast<float*>(smem);
     constexpr int pitch = BM + 4;
     if (warp >= 2) {
-        // the two scales are fetched while the weights stream: their global-load latency (about a microsecond
-        // when they miss L2) would otherwise sit between the last MMA and the first store
-        if (warp == 2 && lane == 0) {
-            if (p.pdl) pdl_wait_prior();               // the scales may be the preceding kernel's output
-            *sc_slot = __ldg(p.scale_a) * __ldg(p.scale_b);
-        }
         bool ok = mbar_wait(tmem_full, 0);
         if (!ok) { *abort_flag = 1; report_timeout(p.status); }
         ok = ok && (*abort_flag == 0);
@@ -240,6 +248,12 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
             for (int c0 = 0; c0 < NB; c0 += 16) {
                 float v[16];
                 tmem_ld16(taddr + c0, v);
+                for (int a = 1; a < p.issuers && a < nkb; a++) {     // the other issuers' accumulators, in order
+                    float w[16];
+                    tmem_ld16(taddr + a * p.acc_stride + c0, w);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) v[j] += w[j];
+                }
 #pragma unroll
                 for (int j = 0; j < 16; j++) col[(c0 + j) * pitch] = v[j];
             }
@@ -386,7 +400,9 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
     p.ring_bytes = ring;
     p.pdl = pdl ? 1 : 0;
     p.trace = g_trace ? g_trace + static_cast<size_t>(g_trace_next++ % g_trace_slots) * 8 : nullptr;
-    p.te_col = NB < 32 ? 32 : NB;
+    p.acc_stride = (NB + 31) / 32 * 32;
+    p.issuers = 2;             // four were measured no faster (the epilogue then adds four accumulators)
+    p.te_col = p.issuers * p.acc_stride;
     p.tmem_cols = 32;
     while (p.tmem_cols < p.te_col + 8 * stages) p.tmem_cols *= 2;
 
