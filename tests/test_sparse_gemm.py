@@ -217,6 +217,38 @@ def test_launches_that_overlap_their_predecessor(cuda_device, oracle, M, N, K, s
 
 
 @pytest.mark.gpu
+def test_step_trace(cuda_device):
+    """rdb_sparse_gemm_trace: the first CTA's eight stamps of a launch are in order (the split-K slot only when the
+    launch splits K) and switching it off stops the writes."""
+    import rocm_dev_b200 as R
+    from rocm_dev_b200 import quant
+    dev = cuda_device
+    M, N, K = 16, 512, 4096
+    Wq, sb = _sparse_weights(N, K, 5)
+    vals, meta = R.pack_2of4(Wq)
+    Aq, sa = quant.quantize_per_tensor(torch.randn((M, K), generator=torch.Generator().manual_seed(6)).bfloat16())
+    args = (Aq.to(dev), vals.to(dev), meta.to(dev), sa.to(dev), sb.to(dev))
+    R.sparse_gemm_fp8(*args, split_k=2)
+    torch.cuda.synchronize()
+    tr = torch.zeros(2 * 8, dtype=torch.int64, device=dev)
+    assert R.lib().rdb_sparse_gemm_trace(tr.data_ptr(), 2) == 0
+    try:
+        R.sparse_gemm_fp8(*args, split_k=2)
+        R.sparse_gemm_fp8(*args, split_k=1)
+        torch.cuda.synchronize()
+    finally:
+        assert R.lib().rdb_sparse_gemm_trace(None, 0) == 0
+    t = tr.cpu().numpy().reshape(2, 8)
+    assert (t[0] > 0).all() and (np.diff(t[0]) >= 0).all()
+    assert t[1][5] == 0 and (np.diff(t[1][[0, 1, 2, 3, 4, 6, 7]]) >= 0).all() and t[1][0] >= t[0][7]
+    tr.zero_()
+    R.sparse_gemm_fp8(*args)
+    torch.cuda.synchronize()
+    assert int(tr.abs().sum().item()) == 0
+    assert R.lib().rdb_sparse_gemm_trace(tr.data_ptr(), 0) == 6
+
+
+@pytest.mark.gpu
 def test_error_codes(cuda_device):
     import rocm_dev_b200 as R
     L = R.lib()
