@@ -251,6 +251,21 @@ int rdb_sparse_gemm_fp8_flags(const uint8_t *A, const uint8_t *Wvals, const uint
  * vals [N,K/2] and meta.  Returns RDB_INVALID_CONFIG if a group of four holds
  * more than two non-zero bytes.  rdb_sparse_meta_bytes gives meta's size (0 for
  * an unsupported shape). */
+/* A list of sparse GEMMs that share the batch size M in ONE launch (a decode
+ * layer's projections): the 128-row tiles of all problems form one grid, so the
+ * CTAs of a later problem start as SMs fall free and nothing of a launch's
+ * fixed chain is paid per GEMM.  All M must be equal (RDB_INVALID_CONFIG
+ * otherwise); N and K may differ; 1 <= count <= RDB_SPARSE_GROUP_MAX.  flags as for
+ * rdb_sparse_gemm_fp8_flags.  Same bits as the single calls with the same K
+ * split (automatic from the total tile count).  No reference counterpart. */
+typedef struct {
+    const uint8_t *A, *Wvals, *Wmeta;
+    const float *scale_a, *scale_b;
+    uint16_t *D;
+    int M, N, K;
+} rdb_sparse_problem;
+#define RDB_SPARSE_GROUP_MAX 8
+int rdb_sparse_gemm_fp8_grouped(const rdb_sparse_problem *problems, int count, unsigned flags, void *stream);
 /* Diagnostics: registers a device buffer of slots x 8 uint64.  While registered,
  * sparse launch i writes %globaltimer stamps of its first CTA (entry, set-up
  * done, first stage full, last stage's MMAs issued, accumulator complete,

@@ -43,6 +43,7 @@ _SIGNATURES = {
     "rdb_sparse_gemm_fp8": (i, [u8p, u8p, u8p, f32p, f32p, vp, i, i, i, vp]),
     "rdb_sparse_gemm_fp8_tuned": (i, [u8p, u8p, u8p, f32p, f32p, vp, i, i, i, i, vp]),
     "rdb_sparse_gemm_trace": (i, [vp, i]),
+    "rdb_sparse_gemm_fp8_grouped": (i, [vp, i, C.c_uint, vp]),
     "rdb_sparse_gemm_fp8_flags": (i, [u8p, u8p, u8p, f32p, f32p, vp, i, i, i, i, C.c_uint, vp]),
     "rdb_sparse_meta_bytes": (C.c_size_t, [i, i]),
     "rdb_sparse_pack_2of4": (i, [vp, i, i, vp, vp]),

@@ -69,6 +69,24 @@ struct Params {
     unsigned long long* trace; // optional: 8 %globaltimer stamps of the launch's first CTA (diagnostics), else nullptr
 };
 
+// A launch computes a LIST of GEMMs that share the batch (M) and the configuration: blockIdx.y walks the 128-row
+// tiles of all problems one after the other, so the CTAs of a later problem start as SMs fall free - no launch gap,
+// and set-up, first loads and epilogues of different CTAs overlap one another's streams.
+constexpr int kMaxProblems = 8;
+struct Prob {
+    CUtensorMap tmW, tmX;
+    __nv_bfloat16* D;
+    const uint8_t* meta;
+    const float* scale_a;
+    const float* scale_b;
+    int N, num_kb, tile_begin;
+};
+struct GParams {
+    Prob prob[kMaxProblems];
+    int count;
+    Params common;             // D, meta, scales, N and num_kb are taken from the CTA's problem
+};
+
 // entry, set-up done, first stage full, last stage's MMAs issued, accumulator complete, partials exchanged, stores issued, exit
 __device__ __forceinline__ void stamp(const Params& p, int slot) {
     if (p.trace && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) p.trace[slot] = globaltimer_ns();
@@ -105,13 +123,25 @@ __device__ __forceinline__ void bulk_load(uint32_t dst_smem, const void* src, ui
 }
 
 __global__ void __launch_bounds__(NUM_THREADS, 1)
-sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ CUtensorMap tmX, const Params p) {
+sparse_gemm_kernel(const __grid_constant__ GParams g) {
+    int pi = 0;
+    while (pi + 1 < g.count && static_cast<int>(blockIdx.y) >= g.prob[pi + 1].tile_begin) pi++;
+    const Prob& pr = g.prob[pi];
+    const CUtensorMap& tmW = pr.tmW;
+    const CUtensorMap& tmX = pr.tmX;
+    Params p = g.common;
+    p.D = pr.D;
+    p.meta = pr.meta;
+    p.scale_a = pr.scale_a;
+    p.scale_b = pr.scale_b;
+    p.N = pr.N;
+    p.num_kb = pr.num_kb;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int S = gridDim.x, rank = blockIdx.x;      // cluster = K slices of one tile
     if (threadIdx.x == 0) stamp(p, 0);
-    const int tile = blockIdx.y, n0 = tile * BM;
+    const int tile = static_cast<int>(blockIdx.y) - pr.tile_begin, n0 = tile * BM;
     const int m0 = blockIdx.z * p.NB;                 // first batch row of this CTA
     const int m_count = p.M - m0 < p.NB ? p.M - m0 : p.NB;
     const int NB = p.NB, nstages = p.nstages;
@@ -198,7 +228,7 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         // k-block into an accumulator of their own; the epilogue adds the accumulators.
         if (lane == 0) {
             const int which = warp - 1;
-            if (which == 1) {
+            if (which == p.issuers - 1) {
                 // the two scales are fetched while the weights stream: their global-load latency (about a microsecond
                 // when they miss L2) would otherwise sit between the last MMA and the first store
                 if (p.pdl) pdl_wait_prior();               // the scales may be the preceding kernel's output
@@ -328,15 +358,25 @@ sparse_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
 static unsigned long long* g_trace = nullptr;
 static int g_trace_slots = 0, g_trace_next = 0;
 
-static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* sa, const float* sb, uint16_t* D,
-               int M, int N, int K, int split_k_hint, unsigned flags, cudaStream_t stream) {
+static int run_list(const rdb_sparse_problem* pr, int count, int split_k_hint, unsigned flags, cudaStream_t stream) {
     if (flags & ~RDB_SKINNY_OVERLAP_PRIOR_KERNEL) return RDB_INVALID_CONFIG;
-    if (M < 1 || N < 1 || K < 1) return RDB_BAD_SHAPE;
-    if (M > 256) return RDB_M_ABOVE_WARPTILE_M;
-    if (N % 2 != 0) return RDB_N_NOT_EVEN;
-    if (K % 256 != 0) return RDB_K_NOT_DIVISIBLE_BY_WARPTILE_K;
-    if (!aligned16(A) || !aligned16(Wvals) || !aligned16(Wmeta) || (reinterpret_cast<uintptr_t>(D) & 3u)) return RDB_BAD_ALIGNMENT;
+    if (!pr || count < 1 || count > kMaxProblems) return RDB_INVALID_CONFIG;
     if (split_k_hint != 0 && split_k_hint != 1 && split_k_hint != 2 && split_k_hint != 4) return RDB_INVALID_CONFIG;
+    const int M = pr[0].M;
+    int tiles = 0, min_kb = 1 << 30;
+    for (int i = 0; i < count; i++) {
+        const rdb_sparse_problem& q = pr[i];
+        if (q.M < 1 || q.N < 1 || q.K < 1) return RDB_BAD_SHAPE;
+        if (q.M > 256) return RDB_M_ABOVE_WARPTILE_M;
+        if (q.M != M) return RDB_INVALID_CONFIG;             // one batch, one configuration per launch
+        if (q.N % 2 != 0) return RDB_N_NOT_EVEN;
+        if (q.K % 256 != 0) return RDB_K_NOT_DIVISIBLE_BY_WARPTILE_K;
+        if (!aligned16(q.A) || !aligned16(q.Wvals) || !aligned16(q.Wmeta) || (reinterpret_cast<uintptr_t>(q.D) & 3u)) return RDB_BAD_ALIGNMENT;
+        if (!q.scale_a || !q.scale_b) return RDB_INVALID_CONFIG;
+        tiles += (q.N + BM - 1) / BM;
+        if (q.K / 256 < min_kb) min_kb = q.K / 256;
+    }
+    if (tiles > 65535) return RDB_SIZE_ABOVE_LIMIT;
     int err = 0;
     DeviceInfo* info = device_info(&err);
     if (!info) return err;
@@ -344,8 +384,6 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
     // dimension: more CTAs, and each re-reads only its own part of the activations.
     const int mblocks = M > 128 ? (M + 127) / 128 : 1;
     const int NB = ((M + mblocks - 1) / mblocks + 15) / 16 * 16;
-    const int tiles = (N + BM - 1) / BM;
-    const int num_kb = K / 256;
     int S = split_k_hint;
     if (S == 0) {
         // resident clusters of 2 / 4 CTAs on a 148-SM part: 74 / 33 (one per SM)
@@ -355,19 +393,24 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
             else if (tiles * mblocks * 2 <= info->sm_count) S = 2;
         }
     }
-    while (S > 1 && (S > num_kb || NB > 64)) S /= 2;
+    while (S > 1 && (S > min_kb || NB > 64)) S /= 2;
     const bool pdl = (flags & RDB_SKINNY_OVERLAP_PRIOR_KERNEL) != 0;
     // A launch that may overlap its predecessor keeps its ring to under half of an SM's shared memory (and, below,
     // its TMEM to half of the columns) when the batch is narrow: its CTAs can then become resident beside the
     // predecessor's and stream their first weights while those are still in their epilogue.
-    const int ring_budget = (pdl && NB <= 32) ? 108 * 1024 : 200 * 1024;   // wider batches: too few stages (measured slower)
+    const int ring_budget = (pdl && NB <= 32) ? 108 * 1024 : SMEM_LIMIT - 1024 - BAR_BYTES;   // wider batches: too few stages (measured slower)
     int stages = (ring_budget - red_bytes(NB, S)) / stage_bytes(NB);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
-    const int kb_per = (num_kb + S - 1) / S;
+    const int kb_per = min_kb / S;
     if (stages > kb_per) stages = kb_per;
     if (stages < 1) stages = 1;
     while (stages > 1 && smem_bytes(NB, S, stages) > SMEM_LIMIT) stages--;
     if (smem_bytes(NB, S, stages) > SMEM_LIMIT) return RDB_SIZE_ABOVE_LIMIT;
+    // Two issuing threads take alternate k-blocks, so the ring depth must be even: each thread then always meets the
+    // same stages and waits for CONSECUTIVE completions of their barriers (a parity wait cannot tell completion n
+    // from n + 2, which an odd depth - or a single stage - would ask of it).  A one-stage ring keeps one issuer.
+    const int issuers = stages >= 2 ? 2 : 1;
+    if (issuers == 2) stages -= stages % 2;
 
     static bool attr_set[kMaxDevices] = {};
     int dev = 0;
@@ -379,20 +422,29 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
         cudaFuncSetAttribute(sparse_gemm_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         attr_set[dev] = true;
     }
-    CUtensorMap tmW, tmX;
-    int r = make_tmap_2d(&tmW, Wvals, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, N, K / 2, K / 2, BKC, BM, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (r != RDB_SUCCESS) return r;
-    r = make_tmap_2d(&tmX, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, K, K, 128, NB, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (r != RDB_SUCCESS) return r;
-    Params p;
-    p.D = reinterpret_cast<__nv_bfloat16*>(D);
-    p.meta = Wmeta;
-    p.scale_a = sa;
-    p.scale_b = sb;
+    GParams g;
+    memset(&g, 0, sizeof(g));
+    g.count = count;
+    int tile_begin = 0;
+    for (int i = 0; i < count; i++) {
+        const rdb_sparse_problem& q = pr[i];
+        Prob& d = g.prob[i];
+        int r = make_tmap_2d(&d.tmW, q.Wvals, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, q.N, q.K / 2, q.K / 2, BKC, BM, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (r != RDB_SUCCESS) return r;
+        r = make_tmap_2d(&d.tmX, q.A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, M, q.K, q.K, 128, NB, CU_TENSOR_MAP_SWIZZLE_128B);
+        if (r != RDB_SUCCESS) return r;
+        d.D = reinterpret_cast<__nv_bfloat16*>(q.D);
+        d.meta = q.Wmeta;
+        d.scale_a = q.scale_a;
+        d.scale_b = q.scale_b;
+        d.N = q.N;
+        d.num_kb = q.K / 256;
+        d.tile_begin = tile_begin;
+        tile_begin += (q.N + BM - 1) / BM;
+    }
+    Params& p = g.common;
     p.status = info->status_dev;
     p.M = M;
-    p.N = N;
-    p.num_kb = num_kb;
     p.NB = NB;
     p.nstages = stages;
     int ring = stages * stage_bytes(NB);
@@ -401,7 +453,7 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
     p.pdl = pdl ? 1 : 0;
     p.trace = g_trace ? g_trace + static_cast<size_t>(g_trace_next++ % g_trace_slots) * 8 : nullptr;
     p.acc_stride = (NB + 31) / 32 * 32;
-    p.issuers = 2;             // four were measured no faster (the epilogue then adds four accumulators)
+    p.issuers = issuers;       // four were measured no faster (the epilogue then adds four accumulators)
     p.te_col = p.issuers * p.acc_stride;
     p.tmem_cols = 32;
     while (p.tmem_cols < p.te_col + 8 * stages) p.tmem_cols *= 2;
@@ -420,7 +472,22 @@ static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, con
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl ? 2 : 1;
-    return cudaLaunchKernelEx(&cfg, sparse_gemm_kernel, tmW, tmX, p) == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
+    return cudaLaunchKernelEx(&cfg, sparse_gemm_kernel, g) == cudaSuccess ? RDB_SUCCESS : RDB_CUDA_ERROR;
+}
+
+static int run(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* sa, const float* sb, uint16_t* D,
+               int M, int N, int K, int split_k_hint, unsigned flags, cudaStream_t stream) {
+    rdb_sparse_problem q;
+    q.A = A;
+    q.Wvals = Wvals;
+    q.Wmeta = Wmeta;
+    q.scale_a = sa;
+    q.scale_b = sb;
+    q.D = D;
+    q.M = M;
+    q.N = N;
+    q.K = K;
+    return run_list(&q, 1, split_k_hint, flags, stream);
 }
 
 }  // namespace sparse
@@ -477,6 +544,10 @@ int rdb_sparse_gemm_fp8(const uint8_t* A, const uint8_t* Wvals, const uint8_t* W
 int rdb_sparse_gemm_fp8_tuned(const uint8_t* A, const uint8_t* Wvals, const uint8_t* Wmeta, const float* scale_a,
                               const float* scale_b, uint16_t* D, int M, int N, int K, int split_k, void* stream) {
     return rdb::sparse::run(A, Wvals, Wmeta, scale_a, scale_b, D, M, N, K, split_k, 0, static_cast<cudaStream_t>(stream));
+}
+
+int rdb_sparse_gemm_fp8_grouped(const rdb_sparse_problem* problems, int count, unsigned flags, void* stream) {
+    return rdb::sparse::run_list(problems, count, 0, flags, static_cast<cudaStream_t>(stream));
 }
 
 int rdb_sparse_gemm_trace(unsigned long long* device_buffer, int slots) {

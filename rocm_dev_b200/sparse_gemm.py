@@ -9,6 +9,8 @@ lowest index), quantise per tensor, store the kept bytes plus 2-bit positions.
 """
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 
 from ._lib import check, lib
@@ -86,3 +88,27 @@ def sparse_gemm_fp8(A: torch.Tensor, vals: torch.Tensor, meta: torch.Tensor, sca
                                               scale_b.data_ptr(), out.data_ptr(), M, N, K, split_k, flags,
                                               torch.cuda.current_stream(A.device).cuda_stream), "rdb_sparse_gemm_fp8")
     return out
+
+
+class SparseProblem(C.Structure):
+    """``rdb_sparse_problem`` of include/rocm_dev_b200.h."""
+    _fields_ = [("A", C.c_void_p), ("Wvals", C.c_void_p), ("Wmeta", C.c_void_p), ("scale_a", C.c_void_p),
+                ("scale_b", C.c_void_p), ("D", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int)]
+
+
+def sparse_gemm_fp8_grouped(problems, flags: int = 0) -> int:
+    """A list of sparse GEMMs with one batch size in ONE launch
+    (rdb_sparse_gemm_fp8_grouped).  ``problems``: up to 8 tuples ``(A, vals,
+    meta, scale_a, scale_b, D)`` of device tensors with the meaning of
+    ``sparse_gemm_fp8``; all A must have the same number of rows.  Returns the
+    status code."""
+    arr = (SparseProblem * len(problems))()
+    for i, (A, vals, meta, sa, sb, D) in enumerate(problems):
+        A = A if A.dtype == torch.uint8 else A.view(torch.uint8)
+        M, K = A.shape
+        assert vals.shape[1] * 2 == K and D.dtype == torch.bfloat16 and D.is_contiguous() and D.shape == (M, vals.shape[0])
+        arr[i] = SparseProblem(A.data_ptr(), vals.data_ptr(), meta.data_ptr(), sa.data_ptr(), sb.data_ptr(), D.data_ptr(),
+                               M, vals.shape[0], K)
+    dev = problems[0][0].device
+    with torch.cuda.device(dev):
+        return int(lib().rdb_sparse_gemm_fp8_grouped(arr, len(problems), flags, torch.cuda.current_stream(dev).cuda_stream))

@@ -217,6 +217,45 @@ def test_launches_that_overlap_their_predecessor(cuda_device, oracle, M, N, K, s
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("M", [8, 64, 200])
+def test_a_list_of_gemms_in_one_launch(cuda_device, oracle, M):
+    """rdb_sparse_gemm_fp8_grouped: problems of different N and K that share the batch - each result equals the
+    oracle's, and the bits of the single call with the same K split; with the overlap flag as well.  Lists whose
+    batch sizes differ, empty lists and over-long lists are refused."""
+    import rocm_dev_b200 as R
+    from rocm_dev_b200 import quant
+    dev = cuda_device
+    shapes = [(384, 1024), (128, 2048), (1000, 1024), (256, 1024)]
+    split = 4 if M <= 64 else 1          # 14 tiles in all: clusters of four for a narrow batch, none for a wide one
+    probs, refs = [], []
+    for i, (N, K) in enumerate(shapes):
+        Wq, sb = _sparse_weights(N, K, 50 + i)
+        vals, meta = R.pack_2of4(Wq)
+        Aq, sa = quant.quantize_per_tensor(torch.randn((M, K), generator=torch.Generator().manual_seed(60 + i)).bfloat16())
+        D = torch.zeros((M, N), dtype=torch.bfloat16, device=dev)
+        probs.append((Aq.to(dev), vals.to(dev), meta.to(dev), sa.to(dev), sb.to(dev), D))
+        refs.append((Aq, Wq, sa, sb, K))
+    for flags in (0, R.OVERLAP_PRIOR_KERNEL):
+        for p in probs:
+            p[5].zero_()
+        assert R.sparse_gemm_fp8_grouped(probs, flags=flags) == 0
+        torch.cuda.synchronize()
+        assert R.lib().rdb_device_status() == 0
+        for (A, vals, meta, sa, sb, D), (Aq, Wq, hsa, hsb, K) in zip(probs, refs):
+            ref = oracle.gemm_fp8_bf16(Aq.numpy(), Wq.numpy(), hsa.item(), hsb.item())
+            ref64, mag = oracle.gemm_fp8_f64(Aq.numpy(), Wq.numpy(), hsa.item(), hsb.item())
+            check_gemm_parity(bf16_bits(D), ref, ref64, mag, K)
+            single = R.sparse_gemm_fp8(A, vals, meta, sa, sb, split_k=split)
+            assert torch.equal(D, single)
+    other = list(probs[0])
+    other[0] = torch.zeros((M + 1, shapes[0][1]), dtype=torch.uint8, device=dev)
+    other[5] = torch.zeros((M + 1, shapes[0][0]), dtype=torch.bfloat16, device=dev)
+    assert R.sparse_gemm_fp8_grouped([probs[1], tuple(other)]) == 6
+    assert R.lib().rdb_sparse_gemm_fp8_grouped(None, 0, 0, None) == 6
+    assert R.sparse_gemm_fp8_grouped(probs * 3) == 6
+
+
+@pytest.mark.gpu
 def test_step_trace(cuda_device):
     """rdb_sparse_gemm_trace: the first CTA's eight stamps of a launch are in order (the split-K slot only when the
     launch splits K) and switching it off stops the writes."""
