@@ -398,7 +398,11 @@ static int run_list(const rdb_sparse_problem* pr, int count, int split_k_hint, u
     // A launch that may overlap its predecessor keeps its ring to under half of an SM's shared memory (and, below,
     // its TMEM to half of the columns) when the batch is narrow: its CTAs can then become resident beside the
     // predecessor's and stream their first weights while those are still in their epilogue.
-    const int ring_budget = (pdl && NB <= 32) ? 108 * 1024 : SMEM_LIMIT - 1024 - BAR_BYTES;   // wider batches: too few stages (measured slower)
+    // So does a grid of more CTAs than the machine has SMs (a list of GEMMs, a tall matrix): with two CTAs resident per
+    // SM the set-up, first loads and epilogue of one overlap the other's stream (a list of 8192 x 8192 matrices at
+    // M = 16 ran a quarter faster per GEMM than with one CTA per SM).
+    const bool many = tiles * S * mblocks > info->sm_count && NB <= 64;
+    const int ring_budget = ((pdl && NB <= 32) || many) ? 108 * 1024 : SMEM_LIMIT - 1024 - BAR_BYTES;   // wider batches: too few stages (measured slower)
     int stages = (ring_budget - red_bytes(NB, S)) / stage_bytes(NB);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
     const int kb_per = min_kb / S;
