@@ -147,7 +147,7 @@ def _check(oracle, dev, M, N, K, seed=0, split_k=0):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,N,K", [(16, 128, 256), (16, 128, 1024), (8, 256, 512), (64, 384, 2048), (256, 256, 1024),
-                                   (100, 200, 768), (1, 2, 256)])
+                                   (100, 200, 768), (1, 2, 256), (16, 20480, 1024), (40, 19200, 512)])
 def test_small_shapes(cuda_device, oracle, M, N, K):
     _check(oracle, cuda_device, M, N, K, seed=M + N)
 
