@@ -13,11 +13,14 @@
 // batch is the MMA N extent (TMEM columns).  Per 128-byte compressed K block
 // (256 logical K) a stage holds: the compressed values (128 x 128 B, TMA,
 // SWIZZLE_128B), two activation boxes (NB x 128 B each), and two 2 KiB metadata
-// atoms ([128 rows][16 B], bulk-copied), which the MMA thread moves into TMEM
+// atoms ([128 rows][16 B], bulk-copied), which an issuing thread moves into TMEM
 // with tcgen05.cp.128x128b before issuing four tcgen05.mma.sp (K = 64 each).
+// Two threads issue (even and odd k-blocks, an accumulator each, added in the
+// epilogue): one thread's per-stage cost, not memory, had set the pace.
 // K may be split over a cluster of 2 or 4 CTAs (small batches); the partials are
 // exchanged through distributed shared memory with st.async and summed in rank
-// order.  Epilogue code is kept compact and cooperative (it runs once per CTA).
+// order.  One launch computes a list of GEMMs that share the batch size
+// (blockIdx.y walks the tiles of all of them); a single call is a list of one.
 #include <cuda_bf16.h>
 
 #include <cstring>
