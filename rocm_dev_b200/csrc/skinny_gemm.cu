@@ -73,6 +73,7 @@ struct Params {
     int nstages;
     int tmem_cols;
     int pdl;         // launched with programmatic stream serialization
+    int mma_m;       // UMMA M for batches of up to 16 rows: 64 (or 128)
     unsigned long long* trace;   // optional [cta][8] %globaltimer stamps (diagnostics), else nullptr
 };
 
@@ -189,7 +190,9 @@ skinny_gemm_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constan
         __syncwarp();
     } else if (warp == 1) {
         if (lane == 0) {
-            const uint32_t idesc = idesc_e4m3_f32(128, R);
+            // 64-row MMAs for batches of up to 16 rows: rows 0-15 of a 64-row accumulator lie in TMEM lanes 0-15, where
+            // the epilogue reads them; half the padded tensor work of a 128-row MMA, hence less power
+            const uint32_t idesc = idesc_e4m3_f32(MPAD == 16 ? p.mma_m : 128, R);
             for (int i = 0; i < nkb; i++) {
                 const int s = i % nstages;
                 const uint32_t ph = (i / nstages) & 1;
@@ -524,6 +527,8 @@ static int run(const uint8_t* A, const uint8_t* B, const float* sa, const float*
     prm.tmem_cols = pl.tmem_cols;
     const bool pdl = (flags & RDB_SKINNY_OVERLAP_PRIOR_KERNEL) != 0;
     prm.pdl = pdl ? 1 : 0;
+    static const bool force128 = [] { const char* v = getenv("RDB_SKINNY_MMA_M"); return v && v[0] == '1'; }();
+    prm.mma_m = force128 ? 128 : 64;
     prm.trace = nullptr;
     if (g_trace && pl.tiles * pl.split_k <= g_trace_ctas) {
         prm.trace = g_trace + static_cast<size_t>(g_trace_next % g_trace_slots) * g_trace_ctas * 12;

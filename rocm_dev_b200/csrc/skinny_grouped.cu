@@ -85,6 +85,7 @@ struct Params {
     unsigned long long* trace;              // optional [grid][4] %globaltimer stamps, else nullptr
     rdb::ar::PushTarget push;               // world > 0: the result goes, block-quantised, to the allreduce staging
     int pdl;                                // launched with programmatic stream serialization (see the launcher)
+    int mma_m;                              // UMMA M: 64 when no problem has more than 16 rows (half the padded work), else 128
 };
 
 __device__ __forceinline__ unsigned ld_acquire_gpu_u32(const unsigned* p) {
@@ -279,7 +280,7 @@ __global__ void __launch_bounds__(NUM_THREADS, 1) skinny_grouped_kernel(const __
                 tc_fence_after_sync();
                 if (i == 0) stamp(p, 1);
                 const uint32_t a = stage0 + s * STAGE, w = a + A_BYTES;
-                const uint32_t idesc = idesc_e4m3_f32(128, pr.R);
+                const uint32_t idesc = idesc_e4m3_f32(p.mma_m, pr.R);
                 const uint32_t d = tmem_base + buf * MAX_R;
 #pragma unroll
                 for (int ks = 0; ks < BK / 32; ks++)
@@ -592,6 +593,15 @@ static int run(const rdb_skinny_problem* pr, int count, cudaStream_t stream, con
     static const bool plain_launch = [] { const char* v = getenv("RDB_GROUPED_PLAIN_LAUNCH"); return v && v[0] == '1'; }();
     const bool pdl = (flags & RDB_SKINNY_OVERLAP_PRIOR_KERNEL) != 0;
     prm.pdl = pdl ? 1 : 0;
+    // 64-row MMAs when every batch fits 16 rows: rows 0-15 of a 64-row accumulator lie in TMEM lanes 0-15, where the
+    // epilogue warps (lanes 0-31) read them; half the padded tensor work, hence less power (RDB_SKINNY_MMA_M=128 keeps 128)
+    prm.mma_m = 128;
+    {
+        bool narrow = true;
+        for (int i = 0; i < count; i++) narrow = narrow && pr[i].M <= 16;
+        static const bool force128 = [] { const char* v = getenv("RDB_SKINNY_MMA_M"); return v && v[0] == '1'; }();
+        if (narrow && !force128) prm.mma_m = 64;
+    }
     cudaLaunchAttribute attr[1];
     if (pdl) {
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
